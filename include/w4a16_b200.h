@@ -1,0 +1,112 @@
+/*
+ * w4a16_b200 -- C ABI of the B200 (sm_100a) W4A16 linear library.
+ *
+ * Packed weight format (shared with the reference project, w4a16/quantization.py:4-113):
+ *   packed  uint8  [N, K/2] row-major; byte j of a row = code(2j) in bits 0-3, code(2j+1) in
+ *           bits 4-7, 4-bit two's complement (all 16 values decode, 0x8 -> -8)
+ *   scales  fp16   [N, K/group_size] row-major, one scale per group_size consecutive k
+ *   x       fp16   [M, K] row-major        y  fp16 [M, N] row-major
+ *   y[m][n] = half( sum_k float(x[m][k]) * code[n][k] * float(scale[n][k/group_size]) )
+ *
+ * Conventions for every entry point:
+ *   - all pointers are DEVICE pointers on the current device unless a name ends in _host;
+ *   - the call enqueues work on `stream` and returns; it never synchronises, allocates or frees;
+ *   - inputs are read-only, outputs are fully overwritten;
+ *   - the return value is W4A16_OK (0) or a negative W4A16_ERR_* code; nothing is launched on error.
+ *
+ * The torch operator shim (nibble_b200/csrc/int4_linear.cpp) binds exactly these functions.
+ */
+#ifndef W4A16_B200_H_
+#define W4A16_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* A cudaStream_t, spelled without the CUDA headers. */
+typedef struct CUstream_st* w4a16_stream_t;
+
+enum {
+    W4A16_OK = 0,
+    W4A16_ERR_NULL_POINTER = -1,  /* a required pointer is NULL                                  */
+    W4A16_ERR_BAD_SHAPE = -2,     /* negative size, odd K, K % group_size != 0                    */
+    W4A16_ERR_BAD_GROUP = -3,     /* group_size <= 0 or odd (dequantize: not a multiple of 32)    */
+    W4A16_ERR_MISALIGNED = -4,    /* a pointer misses the alignment this entry point requires     */
+    W4A16_ERR_WORKSPACE = -5,     /* workspace missing or too small for the requested split       */
+    W4A16_ERR_BAD_CONFIG = -6,    /* an explicit launch configuration is not one the library has  */
+    W4A16_ERR_LAUNCH = -7,        /* the CUDA runtime refused the launch (see cudaGetLastError)   */
+    W4A16_ERR_TOO_LARGE = -8      /* a size exceeds what this entry point supports                */
+};
+
+/* Flags for w4a16_linear_f16. */
+enum {
+    /* Launch with programmatic stream serialisation: the kernel may start, and prefetch packed
+     * weights and scales, while the preceding kernel of the stream is still running; it waits for
+     * that kernel before it reads x or writes y.  Only valid when nothing earlier in the stream
+     * that may still be running writes `packed` or `scales`. */
+    W4A16_FLAG_PROGRAMMATIC_LAUNCH = 1u << 0,
+    /* Route to the generic kernel even when the fast path applies (testing / A-B). */
+    W4A16_FLAG_FORCE_GENERIC = 1u << 1
+};
+
+/* Explicit launch shape of the fused tensor-core kernel; zero fields mean "choose for me". */
+typedef struct w4a16_linear_config {
+    int32_t row_tiles;   /* 16-row tiles owned by one warp: 1, 2 or 4                             */
+    int32_t k_warps;     /* warps of a CTA that split K between them: 4 or 8                       */
+    int32_t k_splits;    /* CTAs that split K of one row block (>1 needs the workspace)            */
+    int32_t unroll;      /* 128-wide K chunks fetched per warp per pipeline step: 1, 2 or 4        */
+} w4a16_linear_config;
+
+/*
+ * Fused unpack + dequantise + matmul:  y = x . dequant(packed, scales)^T.
+ * Replaces the reference's int4_linear_cuda (csrc/int4_linear_kernel.cu:641-802) and the kernels
+ * it dispatches to (decode_multirow :325-404, small_batch :542-617, naive :20-69).
+ *
+ * Fast path (tensor-core kernel) when group_size == 128 and x, packed are 16-byte aligned;
+ * otherwise a generic kernel that accepts any even group_size and any alignment.
+ * `workspace` may be NULL (then K is never split across CTAs); if given it must be 16-byte aligned,
+ * hold at least w4a16_linear_workspace_bytes(M, N, K) bytes, be zero-filled before its first use
+ * and not be shared by calls that may run concurrently.  The library leaves it ready for re-use.
+ * M == 0 or N == 0 returns W4A16_OK without launching.
+ */
+int w4a16_linear_f16(const void* x, const void* packed, const void* scales, void* y,
+                     int64_t M, int64_t N, int64_t K, int64_t group_size,
+                     void* workspace, size_t workspace_bytes,
+                     uint32_t flags, w4a16_stream_t stream);
+
+/* Same as w4a16_linear_f16 with an explicit launch shape for the fast path (tuning, tests).
+ * Returns W4A16_ERR_BAD_CONFIG when the fast path does not apply or the shape is not built. */
+int w4a16_linear_f16_config(const void* x, const void* packed, const void* scales, void* y,
+                            int64_t M, int64_t N, int64_t K, int64_t group_size,
+                            void* workspace, size_t workspace_bytes,
+                            uint32_t flags, const w4a16_linear_config* config,
+                            w4a16_stream_t stream);
+
+/* Bytes of workspace that let w4a16_linear_f16 split K across CTAs for this problem
+ * (FP32 partial sums plus arrival counters).  Never fails; returns 0 for empty problems. */
+size_t w4a16_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
+
+/*
+ * packed + scales -> FP16 [N, K], bit-identical to half(float(code) * float(scale)).
+ * Replaces the reference's int4_dequantize_cuda (csrc/int4_linear_kernel.cu:805-867).
+ * Requires group_size a positive multiple of 32 and `packed` 16-byte aligned, as the reference does.
+ */
+int w4a16_dequantize_f16(const void* packed, const void* scales, void* weights,
+                         int64_t N, int64_t K, int64_t group_size, w4a16_stream_t stream);
+
+/* Number of kernels this library has launched in this process (all entry points, all devices). */
+uint64_t w4a16_launch_count(void);
+
+/* Static description of an error code. */
+const char* w4a16_status_string(int status);
+
+/* ABI version: bumped when a signature above changes. */
+int w4a16_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* W4A16_B200_H_ */

@@ -1,0 +1,75 @@
+"""Loaders for the two native libraries built by ``nibble_b200._build``.
+
+``core()`` returns a ``ctypes.CDLL`` for ``libw4a16_b200.so`` with argument types set for every
+function declared in ``include/w4a16_b200.h``; ``load_torch_ops()`` loads ``_C.so`` so that
+``torch.ops.w4a16.*`` exist.  Neither builds anything and neither has a fallback: a missing
+library is an error the caller sees.
+"""
+from __future__ import annotations
+
+import ctypes
+import functools
+import pathlib
+
+PKG = pathlib.Path(__file__).resolve().parent
+CORE_LIB = PKG / "libw4a16_b200.so"
+TORCH_LIB = PKG / "_C.so"
+
+
+class LinearConfig(ctypes.Structure):
+    """Mirror of ``w4a16_linear_config``; zero fields mean "library's choice"."""
+
+    _fields_ = [
+        ("row_tiles", ctypes.c_int32),
+        ("k_warps", ctypes.c_int32),
+        ("k_splits", ctypes.c_int32),
+        ("unroll", ctypes.c_int32),
+    ]
+
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int64
+
+# name -> (restype, argtypes): the complete exported surface of include/w4a16_b200.h
+C_API = {
+    "w4a16_linear_f16": (ctypes.c_int, [_P, _P, _P, _P, _I, _I, _I, _I, _P, ctypes.c_size_t, ctypes.c_uint32, _P]),
+    "w4a16_linear_f16_config": (
+        ctypes.c_int,
+        [_P, _P, _P, _P, _I, _I, _I, _I, _P, ctypes.c_size_t, ctypes.c_uint32, ctypes.POINTER(LinearConfig), _P],
+    ),
+    "w4a16_linear_workspace_bytes": (ctypes.c_size_t, [_I, _I, _I]),
+    "w4a16_dequantize_f16": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
+    "w4a16_launch_count": (ctypes.c_uint64, []),
+    "w4a16_status_string": (ctypes.c_char_p, [ctypes.c_int]),
+    "w4a16_abi_version": (ctypes.c_int, []),
+}
+
+FLAG_PROGRAMMATIC_LAUNCH = 1 << 0
+FLAG_FORCE_GENERIC = 1 << 1
+
+
+@functools.lru_cache(maxsize=None)
+def core() -> ctypes.CDLL:
+    if not CORE_LIB.exists():
+        raise RuntimeError(
+            f"{CORE_LIB.name} is not built; run `python -m nibble_b200._build` (needs nvcc)"
+        )
+    lib = ctypes.CDLL(str(CORE_LIB))
+    for name, (restype, argtypes) in C_API.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+def status_string(status: int) -> str:
+    return core().w4a16_status_string(status).decode()
+
+
+@functools.lru_cache(maxsize=None)
+def load_torch_ops() -> None:
+    if not TORCH_LIB.exists():
+        raise ImportError(f"{TORCH_LIB.name} is not built; run `python -m nibble_b200._build`")
+    import torch
+
+    torch.ops.load_library(str(TORCH_LIB))

@@ -1,0 +1,124 @@
+// extern "C" boundary of libw4a16_b200: argument validation and kernel routing only.
+// The declarations, their contracts and the reference functions they replace are in
+// include/w4a16_b200.h.
+#include <cuda_runtime.h>
+
+#include "kernels.h"
+
+namespace w4a16 {
+std::atomic<uint64_t> g_launch_count{0};
+}
+
+namespace {
+
+bool aligned16(const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+int validate_linear(const void* x, const void* packed, const void* scales, const void* y, int64_t M,
+                    int64_t N, int64_t K, int64_t group) {
+    if (M < 0 || N < 0 || K < 0 || (K & 1)) return W4A16_ERR_BAD_SHAPE;
+    if (group <= 0 || (group & 1)) return W4A16_ERR_BAD_GROUP;
+    if (K % group != 0) return W4A16_ERR_BAD_SHAPE;
+    if (M == 0 || N == 0) return W4A16_OK;
+    if (y == nullptr) return W4A16_ERR_NULL_POINTER;
+    if (K > 0 && (x == nullptr || packed == nullptr || scales == nullptr)) return W4A16_ERR_NULL_POINTER;
+    return W4A16_OK;
+}
+
+bool fast_path_applies(const void* x, const void* packed, int64_t K, int64_t group) {
+    return group == w4a16::kGroupFast && K > 0 && aligned16(x) && aligned16(packed);
+}
+
+}  // namespace
+
+extern "C" {
+
+int w4a16_abi_version(void) { return 1; }
+
+uint64_t w4a16_launch_count(void) { return w4a16::g_launch_count.load(std::memory_order_relaxed); }
+
+const char* w4a16_status_string(int status) {
+    switch (status) {
+        case W4A16_OK: return "ok";
+        case W4A16_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case W4A16_ERR_BAD_SHAPE: return "invalid shape: sizes must be non-negative, K even and divisible by group_size";
+        case W4A16_ERR_BAD_GROUP: return "invalid group_size for this entry point";
+        case W4A16_ERR_MISALIGNED: return "a pointer misses the required 16-byte alignment";
+        case W4A16_ERR_WORKSPACE: return "workspace missing or too small";
+        case W4A16_ERR_BAD_CONFIG: return "launch configuration not available";
+        case W4A16_ERR_LAUNCH: return "CUDA kernel launch failed";
+        case W4A16_ERR_TOO_LARGE: return "problem size exceeds what this entry point supports";
+        default: return "unknown status";
+    }
+}
+
+size_t w4a16_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0 || K % w4a16::kGroupFast != 0) return 0;
+    const w4a16_linear_config c = w4a16::choose_linear_config(M, N, K, w4a16::kMaxKSplits);
+    return w4a16::linear_workspace_bytes_for(M, N, c.k_splits);
+}
+
+int w4a16_linear_f16(const void* x, const void* packed, const void* scales, void* y, int64_t M, int64_t N,
+                     int64_t K, int64_t group_size, void* workspace, size_t workspace_bytes, uint32_t flags,
+                     w4a16_stream_t stream) {
+    const int status = validate_linear(x, packed, scales, y, M, N, K, group_size);
+    if (status != W4A16_OK || M == 0 || N == 0) return status;
+    w4a16::LinearProblem p{static_cast<const __half*>(x), static_cast<const uint8_t*>(packed),
+                           static_cast<const __half*>(scales), static_cast<__half*>(y), M, N, K, group_size,
+                           workspace, workspace_bytes};
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (K == 0) {
+        return cudaMemsetAsync(y, 0, static_cast<size_t>(M) * N * sizeof(__half), s) == cudaSuccess
+                   ? W4A16_OK
+                   : W4A16_ERR_LAUNCH;
+    }
+    if ((flags & W4A16_FLAG_FORCE_GENERIC) || !fast_path_applies(x, packed, K, group_size)) {
+        return w4a16::launch_linear_generic(p, s);
+    }
+    // Split K across CTAs only as far as the caller's workspace allows.
+    int max_splits = 1;
+    if (workspace != nullptr && aligned16(workspace)) {
+        for (int splits = w4a16::kMaxKSplits; splits > 1; splits >>= 1) {
+            if (workspace_bytes >= w4a16::linear_workspace_bytes_for(M, N, splits)) {
+                max_splits = splits;
+                break;
+            }
+        }
+    }
+    const w4a16_linear_config cfg = w4a16::choose_linear_config(M, N, K, max_splits);
+    return w4a16::launch_linear_mma(p, cfg, (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0, s);
+}
+
+int w4a16_linear_f16_config(const void* x, const void* packed, const void* scales, void* y, int64_t M,
+                            int64_t N, int64_t K, int64_t group_size, void* workspace,
+                            size_t workspace_bytes, uint32_t flags, const w4a16_linear_config* config,
+                            w4a16_stream_t stream) {
+    const int status = validate_linear(x, packed, scales, y, M, N, K, group_size);
+    if (status != W4A16_OK || M == 0 || N == 0) return status;
+    if (config == nullptr) return W4A16_ERR_NULL_POINTER;
+    if (!fast_path_applies(x, packed, K, group_size)) return W4A16_ERR_BAD_CONFIG;
+    w4a16_linear_config cfg = w4a16::choose_linear_config(M, N, K, 1);
+    if (config->row_tiles) cfg.row_tiles = config->row_tiles;
+    if (config->k_warps) cfg.k_warps = config->k_warps;
+    if (config->k_splits) cfg.k_splits = config->k_splits;
+    if (config->unroll) cfg.unroll = config->unroll;
+    w4a16::LinearProblem p{static_cast<const __half*>(x), static_cast<const uint8_t*>(packed),
+                           static_cast<const __half*>(scales), static_cast<__half*>(y), M, N, K, group_size,
+                           workspace, workspace_bytes};
+    return w4a16::launch_linear_mma(p, cfg, (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0,
+                                    reinterpret_cast<cudaStream_t>(stream));
+}
+
+int w4a16_dequantize_f16(const void* packed, const void* scales, void* weights, int64_t N, int64_t K,
+                         int64_t group_size, w4a16_stream_t stream) {
+    if (N < 0 || K < 0 || (K & 1)) return W4A16_ERR_BAD_SHAPE;
+    if (group_size <= 0 || group_size % 32 != 0) return W4A16_ERR_BAD_GROUP;
+    if (K % group_size != 0) return W4A16_ERR_BAD_SHAPE;
+    if (N == 0 || K == 0) return W4A16_OK;
+    if (packed == nullptr || scales == nullptr || weights == nullptr) return W4A16_ERR_NULL_POINTER;
+    if (!aligned16(packed) || !aligned16(weights)) return W4A16_ERR_MISALIGNED;
+    return w4a16::launch_dequantize(static_cast<const uint8_t*>(packed), static_cast<const __half*>(scales),
+                                    static_cast<__half*>(weights), N, K, group_size,
+                                    reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

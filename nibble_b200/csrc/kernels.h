@@ -1,0 +1,49 @@
+// Internal interface between the C-ABI layer (capi.cu) and the kernel translation units.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+
+#include "../../include/w4a16_b200.h"
+
+namespace w4a16 {
+
+// Kernels launched by this library since it was loaded.
+extern std::atomic<uint64_t> g_launch_count;
+
+constexpr int kGroupFast = 128;        // group size the tensor-core kernel is built for
+constexpr int kMaxKSplits = 8;          // upper bound on CTAs splitting K of one row block
+constexpr int kBatchPerTile = 8;        // batch rows covered by one n8 MMA tile
+constexpr int kMaxBatchTiles = 4;       // n8 tiles per warp (so up to 32 batch rows per CTA pass)
+
+struct LinearProblem {
+    const __half* x;          // [M, K]
+    const uint8_t* packed;    // [N, K/2]
+    const __half* scales;     // [N, K/group]
+    __half* y;                // [M, N]
+    int64_t M, N, K, group;
+    void* workspace;          // may be null
+    size_t workspace_bytes;
+};
+
+// Workspace layout for split-K: arrival counters first, FP32 partials after them.
+size_t linear_counter_bytes(int64_t M, int64_t N);
+size_t linear_workspace_bytes_for(int64_t M, int64_t N, int splits);
+
+// Picks a launch shape for the tensor-core kernel.  `max_splits` caps k_splits (1 = no workspace).
+w4a16_linear_config choose_linear_config(int64_t M, int64_t N, int64_t K, int max_splits);
+
+// Tensor-core path: requires group == 128 and 16-byte aligned x / packed.  Returns a W4A16_* code.
+int launch_linear_mma(const LinearProblem& p, const w4a16_linear_config& cfg, bool programmatic,
+                      cudaStream_t stream);
+
+// Any even group size, any alignment, any M.
+int launch_linear_generic(const LinearProblem& p, cudaStream_t stream);
+
+int launch_dequantize(const uint8_t* packed, const __half* scales, __half* weights, int64_t N,
+                      int64_t K, int64_t group, cudaStream_t stream);
+
+}  // namespace w4a16

@@ -1,0 +1,75 @@
+"""Python entry points of the CUDA operators (same surface as the reference's w4a16/cuda.py:1-83).
+
+``torch.ops.w4a16.linear`` and ``torch.ops.w4a16.dequantize`` are registered by the native shim
+``_C.so``; this module loads it, registers the shape-only fake kernels ``torch.compile`` needs, and
+exposes ``linear_cuda`` / ``dequantize_cuda`` / ``cuda_extension_available``.  There is no
+non-CUDA implementation behind these functions: without the built extension they raise.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native
+
+try:
+    _native.load_torch_ops()
+except (ImportError, OSError) as error:  # not built, or built against another torch
+    _EXTENSION_LOAD_ERROR: Exception | None = error
+else:
+    _EXTENSION_LOAD_ERROR = None
+
+
+if _EXTENSION_LOAD_ERROR is None:
+
+    @torch.library.register_fake("w4a16::linear")
+    def _linear_fake(activations, packed_weights, scales, group_size):
+        # [M, K] x [N, K/2] -> [M, N], dtype of the activations
+        return activations.new_empty((activations.shape[0], packed_weights.shape[0]))
+
+    @torch.library.register_fake("w4a16::dequantize")
+    def _dequantize_fake(packed_weights, scales, group_size):
+        # [N, K/2] -> FP16 [N, K]
+        return packed_weights.new_empty(
+            (packed_weights.shape[0], packed_weights.shape[1] * 2), dtype=torch.float16
+        )
+
+
+def cuda_extension_available() -> bool:
+    """True when the compiled operator library loaded."""
+    return _EXTENSION_LOAD_ERROR is None
+
+
+def _require_extension() -> None:
+    if _EXTENSION_LOAD_ERROR is not None:
+        raise RuntimeError(
+            "The W4A16 CUDA extension is not built. Build it with `python -m nibble_b200._build`."
+        ) from _EXTENSION_LOAD_ERROR
+
+
+def linear_cuda(
+    activations: torch.Tensor,
+    packed_weights: torch.Tensor,
+    scales: torch.Tensor,
+    group_size: int = 128,
+) -> torch.Tensor:
+    """FP16 ``[M, K]`` x packed INT4 ``[N, K/2]`` -> FP16 ``[M, N]`` on the current CUDA stream.
+
+    ``group_size == 128`` with 16-byte aligned activations and weights runs the fused tensor-core
+    kernel for every M; other even group sizes or misaligned tensors run the generic kernel.
+    Invalid arguments raise ``RuntimeError``.
+    """
+    _require_extension()
+    return torch.ops.w4a16.linear(activations, packed_weights, scales, group_size)
+
+
+def dequantize_cuda(
+    packed_weights: torch.Tensor,
+    scales: torch.Tensor,
+    group_size: int = 128,
+) -> torch.Tensor:
+    """Packed INT4 ``[N, K/2]`` -> FP16 ``[N, K]``, bit-identical to ``half(float(code) * float(scale))``.
+
+    Needs ``group_size`` to be a positive multiple of 32 and 16-byte aligned packed weights.
+    """
+    _require_extension()
+    return torch.ops.w4a16.dequantize(packed_weights, scales, group_size)

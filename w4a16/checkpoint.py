@@ -1,0 +1,4 @@
+from nibble_b200.checkpoint import *  # noqa: F401,F403
+from nibble_b200 import checkpoint as _impl
+
+globals().update({k: v for k, v in vars(_impl).items() if not k.startswith("__")})
