@@ -1,0 +1,466 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A16 linear path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl product|reference]
+
+One JSON line on stdout; progress on stderr.
+
+Workload (``config.workload = "tinyllama_decode_linears_m1"``): the 155 W4A16 linears one
+TinyLlama-1.1B decode token passes through (22 blocks x {q,k,v,o,gate,up,down} + lm_head), M=1,
+group 128, every layer instance with its own seeded N(0, 0.02) weights quantised by the package's
+quantiser -- 535 MB of packed weights and scales, four times the L2, so every step streams from
+DRAM.  One *step* is one pass over the 155 layers.  Metric: algorithmic bytes moved per second
+(``N*K/2 + N*K/128*2 + M*K*2 + M*N*2`` per layer -- the payload the reference's profiler counts,
+scripts/profile_kernel.py:310-323).
+
+* ``value``  -- steps replayed from a CUDA graph of ``torch.ops.w4a16.linear`` calls, activations
+  resident in HBM; CUDA events around exactly K replays, max over ranks.
+* ``e2e``    -- the same graph, but every step first copies all activations from pinned host
+  memory and afterwards copies all outputs back to pinned host memory.
+* ``roofline`` -- the fused kernel's bytes per launch over its mean launch duration inside the
+  timed region, against the measured HBM copy bandwidth.
+* ``cpu_baseline`` -- the CPU restatement of the reference's PyTorch path on the host cores.
+* ``layers`` -- per-shape latency of isolated launches over rotating weight copies (> 2x L2 per
+  graph replay), M=1 and M=8, next to cuBLAS FP16 on the dequantised weights.
+
+With N > 1 (torchrun) every rank runs an independent replica of the same workload on its own GPU
+(layers this small are not worth sharding); the job value is the sum.
+
+``--impl reference`` times the CPU restatement alone, one decoder block per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import pathlib
+import statistics
+import sys
+import threading
+import time
+
+ROOT = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+GROUP = 128
+TINYLLAMA = {  # name: (K, N)
+    "qo_proj": (2048, 2048),
+    "kv_proj": (2048, 256),
+    "gate_up_proj": (2048, 5632),
+    "down_proj": (5632, 2048),
+    "lm_head": (2048, 32000),
+}
+LLAMA70B = {
+    "qo_proj": (8192, 8192),
+    "kv_proj": (8192, 1024),
+    "gate_up_proj": (8192, 28672),
+    "down_proj": (28672, 8192),
+}
+BLOCK_ORDER = ["qo_proj", "kv_proj", "kv_proj", "qo_proj", "gate_up_proj", "gate_up_proj", "down_proj"]
+N_BLOCKS = 22
+
+
+def log(*parts) -> None:
+    print(*parts, file=sys.stderr, flush=True)
+
+
+def algorithmic_bytes(m: int, k: int, n: int) -> int:
+    return n * k // 2 + n * (k // GROUP) * 2 + m * k * 2 + m * n * 2
+
+
+def decode_token_layers() -> list[tuple[str, int, int]]:
+    layers = []
+    for _ in range(N_BLOCKS):
+        layers += [(name, *TINYLLAMA[name]) for name in BLOCK_ORDER]
+    layers.append(("lm_head", *TINYLLAMA["lm_head"]))
+    return layers
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while ``active`` is set."""
+
+    REASONS = {
+        0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
+        0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+        0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
+    }
+
+    def __init__(self, index: int, period_s: float = 0.05):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples: list[tuple[int, int]] = []
+        self.max_mhz = None
+        self.active = threading.Event()
+        self.stop = threading.Event()
+        self.error = None
+
+    def run(self) -> None:
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+            while not self.stop.is_set():
+                if self.active.is_set():
+                    mhz = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+                    try:
+                        reasons = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                    except Exception:
+                        reasons = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                    self.samples.append((mhz, reasons))
+                time.sleep(self.period)
+        except Exception as error:  # NVML missing: report, never fail the bench
+            self.error = repr(error)
+
+    def summary(self, window: str) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0,
+                    "window": window, "error": self.error}
+        mask = 0
+        for _, reasons in self.samples:
+            mask |= reasons
+        names = sorted(name for bit, name in self.REASONS.items() if mask & bit and name != "gpu_idle")
+        return {"sm_mhz": statistics.median(mhz for mhz, _ in self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": names, "samples": len(self.samples), "window": window}
+
+
+# ----------------------------------------------------------------------------- product arm
+def make_layer(torch, k: int, n: int, seed: int, device):
+    from nibble_b200 import quantize_and_pack_weights
+
+    g = torch.Generator(device=device).manual_seed(seed)
+    w = torch.randn((n, k), dtype=torch.float32, device=device, generator=g) * 0.02
+    return quantize_and_pack_weights(w, GROUP)
+
+
+def capture(torch, fn):
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    torch.cuda.synchronize()
+    return graph
+
+
+def time_replays(torch, graph, replays: int) -> float:
+    """Milliseconds for `replays` back-to-back replays, CUDA events on the current stream."""
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(replays):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end)
+
+
+def per_shape_table(torch, shapes: dict, m: int, device, l2_bytes: int, with_cublas: bool) -> dict:
+    """Reference method (scripts/profile_kernel.py:334-339,463-551): a graph of back-to-back calls,
+    each on a different weight copy, one replay touching more than twice the L2; median of 20."""
+    from nibble_b200 import dequantize_cuda, linear_cuda
+
+    out = {}
+    peak, _ = measured_peaks()
+    for index, (name, (k, n)) in enumerate(shapes.items()):
+        packed, scales = make_layer(torch, k, n, seed=index, device=device)
+        w_bytes = packed.numel() + scales.numel() * 2
+        copies = max(2, -(-2 * l2_bytes // w_bytes))
+        calls = max(100, copies)
+        pk = packed.unsqueeze(0).repeat(copies, 1, 1)
+        sc = scales.unsqueeze(0).repeat(copies, 1, 1)
+        x = torch.randn((m, k), device=device).half()
+
+        def ours():
+            for i in range(calls):
+                linear_cuda(x, pk[i % copies], sc[i % copies], GROUP)
+
+        graph = capture(torch, ours)
+        us = statistics.median(time_replays(torch, graph, 1) * 1000.0 / calls for _ in range(20))
+        payload = algorithmic_bytes(m, k, n)
+        row = {"us": round(us, 3), "gbs": round(payload / us / 1e3, 1),
+               "frac_measured": round(payload / us / 1e3 / peak, 3), "frac_8tbs": round(payload / us / 1e3 / 8000, 3)}
+        del graph
+        if with_cublas:
+            w16 = dequantize_cuda(packed, scales, GROUP)
+            c16 = max(2, -(-2 * l2_bytes // (w16.numel() * 2)))
+            w16 = w16.unsqueeze(0).repeat(c16, 1, 1)
+            calls16 = max(50, c16)
+
+            def cublas():
+                for i in range(calls16):
+                    torch.nn.functional.linear(x, w16[i % c16])
+
+            graph = capture(torch, cublas)
+            us16 = statistics.median(time_replays(torch, graph, 1) * 1000.0 / calls16 for _ in range(10))
+            row["cublas_fp16_us"] = round(us16, 3)
+            row["speedup_vs_cublas_fp16"] = round(us16 / us, 2)
+            del graph, w16
+        out[name] = row
+        del pk, sc
+        torch.cuda.empty_cache()
+        log(f"  M={m} {name} K={k} N={n}: {row}")
+    return out
+
+
+def cpu_pass(torch, layers, sample_name: str, repeats: int) -> dict:
+    """Times the CPU restatement on `layers` (list of (name, K, N)); returns GB/s over the sample."""
+    from nibble_b200 import quantize_and_pack_weights
+    from oracle import torch_cpu_port as port
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    data = []
+    for index, (_, k, n) in enumerate(layers):
+        g = torch.Generator().manual_seed(index)
+        w = torch.randn((n, k), dtype=torch.float32, generator=g) * 0.02
+        packed, scales = quantize_and_pack_weights(w, GROUP)
+        x = torch.randn((1, k), dtype=torch.float32, generator=g).half()
+        data.append((x, packed, scales))
+    total_bytes = sum(algorithmic_bytes(1, k, n) for _, k, n in layers)
+
+    def one_pass():
+        for x, packed, scales in data:
+            port.linear(x, packed, scales, GROUP)
+
+    one_pass()
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        one_pass()
+        times.append(time.perf_counter() - t0)
+    seconds = statistics.median(times)
+    return {"value": round(total_bytes / seconds / 1e9, 3), "unit": "GB/s", "cores": torch.get_num_threads(),
+            "kind": "port", "sample": sample_name, "seconds_per_sample": round(seconds, 4)}
+
+
+def run_product(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    from nibble_b200 import _native, cuda_extension_available, linear_cuda
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this package has no CPU path")
+    if not cuda_extension_available():
+        raise SystemExit("the CUDA extension is not built: run `python -m nibble_b200._build`")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    if args.pdl:
+        os.environ["W4A16_PDL"] = "1"
+
+    sampler = ClockSampler(local)
+    sampler.start()
+
+    layers = decode_token_layers()
+    log(f"[rank {rank}] building {len(layers)} quantised layers on {torch.cuda.get_device_name(device)}")
+    weights = [make_layer(torch, k, n, seed=1000 * rank + i, device=device) for i, (_, k, n) in enumerate(layers)]
+    g = torch.Generator().manual_seed(1)
+    x_host = [torch.randn((1, k), dtype=torch.float32, generator=g).half().pin_memory() for _, k, _ in layers]
+    x_dev = [x.to(device) for x in x_host]
+    step_bytes = sum(algorithmic_bytes(1, k, n) for _, k, n in layers)
+    outs: list = [None] * len(layers)
+
+    def step():
+        for i, (packed, scales) in enumerate(weights):
+            outs[i] = linear_cuda(x_dev[i], packed, scales, GROUP)
+
+    lib = _native.core()
+    graph = capture(torch, step)
+    # ---- parity gate before any timing: first, a ragged middle one and the last layer vs the oracle
+    from oracle import w4a16_oracle as oracle
+
+    graph.replay()
+    torch.cuda.synchronize()
+    for i in (0, 6, len(layers) - 1):
+        packed, scales = weights[i]
+        rows = slice(0, 512)
+        exact = oracle.linear_fp64(x_host[i].numpy(), packed[rows].cpu().numpy(), scales[rows].cpu().numpy(), GROUP)
+        bound = oracle.error_bound(x_host[i].numpy(), packed[rows].cpu().numpy(), scales[rows].cpu().numpy(), GROUP)
+        err = abs(outs[i][:, rows].double().cpu().numpy() - exact)
+        assert (err <= bound).all(), f"parity gate failed on layer {i}"
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- value: K graph replays, inputs resident
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    barrier()
+    sampler.active.set()
+    launches_before = lib.w4a16_launch_count()
+    ms = time_replays(torch, graph, args.steps)
+    barrier()
+    ms = max_over_ranks(ms)
+    ms_per_step = ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+    kernel_us = ms_per_step * 1e3 / len(layers)
+
+    # ---- e2e: host activations in, host outputs back, every step
+    y_host = [torch.empty((1, n), dtype=torch.float16).pin_memory() for _, _, n in layers]
+    h2d = sum(x.numel() * 2 for x in x_host)
+    d2h = sum(y.numel() * 2 for y in y_host)
+
+    def e2e_step():
+        for dst, src in zip(x_dev, x_host):
+            dst.copy_(src, non_blocking=True)
+        graph.replay()
+        for dst, src in zip(y_host, outs):
+            dst.copy_(src, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        e2e_step()
+    end.record()
+    barrier()
+    e2e_ms = max_over_ranks(start.elapsed_time(end)) / args.steps
+    e2e_value = world * step_bytes / (e2e_ms * 1e-3) / 1e9
+
+    # keep the GPU under the same load long enough for the clock sampler when K is small
+    window = "timed region"
+    if ms + e2e_ms * args.steps < 1500.0:
+        window = "timed region + identical load loop"
+        deadline = time.perf_counter() + 1.5
+        while time.perf_counter() < deadline:
+            for _ in range(50):
+                graph.replay()
+            torch.cuda.synchronize()
+    sampler.active.clear()
+    clocks = sampler.summary(window)
+
+    peak, peak_kind = measured_peaks()
+    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    result = {
+        "metric": "w4a16_linear_hbm_gbs_m1", "value": round(value, 1), "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic (seeded N(0,0.02) weights, N(0,1) activations)",
+        "config": {"workload": "tinyllama_decode_linears_m1", "layers_per_step": len(layers), "M": 1,
+                   "group_size": GROUP, "bytes_per_step": step_bytes, "l2_policy": "inputs larger than L2 (535 MB per step)",
+                   "parallelism": "replicas" if world > 1 else "single", "programmatic_launch": bool(args.pdl)},
+        "decode_tok_s_linears_only": round(world * 1e3 / ms_per_step, 1),
+        "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": round(e2e_ms, 5)},
+        "gpu_launches": args.steps * len(layers),
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "peak_kind": peak_kind, "frac_of_8tbs": round(achieved / 8000, 4),
+                     "traffic": None, "kernel": "linear_mma_kernel", "mean_launch_us": round(kernel_us, 3),
+                     "bytes_per_launch": step_bytes // len(layers)},
+        "clocks": clocks,
+    }
+    assert lib.w4a16_launch_count() >= launches_before  # replays re-run captured nodes; capture itself counted
+
+    if rank == 0 and world == 1 and not args.quick:
+        l2 = torch.cuda.get_device_properties(device).L2_cache_size
+        del graph
+        weights.clear()
+        torch.cuda.empty_cache()
+        log("per-shape latency, rotating weight copies (TinyLlama shapes)")
+        result["layers"] = {
+            "tinyllama_m1": per_shape_table(torch, TINYLLAMA, 1, device, l2, with_cublas=True),
+            "tinyllama_m8": per_shape_table(torch, TINYLLAMA, 8, device, l2, with_cublas=True),
+            "llama70b_m1": per_shape_table(torch, LLAMA70B, 1, device, l2, with_cublas=False),
+            "llama70b_m8": per_shape_table(torch, LLAMA70B, 8, device, l2, with_cublas=True),
+        }
+    if rank == 0 and world == 1:
+        block = [(name, *TINYLLAMA[name]) for name in BLOCK_ORDER]
+        result["cpu_baseline"] = cpu_pass(torch, block * 4, "4 decoder blocks (28 linears) of the workload, M=1", repeats=5)
+    sampler.stop.set()
+    if world > 1:
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
+# ----------------------------------------------------------------------------- reference arm
+def run_reference(args) -> dict:
+    """The reference's CPU path (restated in oracle/torch_cpu_port.py) on the host cores."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return {}
+    import torch
+
+    block = [(name, *TINYLLAMA[name]) for name in BLOCK_ORDER]
+    from nibble_b200 import quantize_and_pack_weights
+    from oracle import torch_cpu_port as port
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    data = []
+    for index, (_, k, n) in enumerate(block):
+        g = torch.Generator().manual_seed(index)
+        packed, scales = quantize_and_pack_weights(torch.randn((n, k), generator=g) * 0.02, GROUP)
+        data.append((torch.randn((1, k), generator=g).half(), packed, scales))
+    step_bytes = sum(algorithmic_bytes(1, k, n) for _, k, n in block)
+
+    def step():
+        for x, packed, scales in data:
+            port.linear(x, packed, scales, GROUP)
+
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    ms_per_step = (time.perf_counter() - t0) * 1e3 / args.steps
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+    sample = "one decoder block (7 linears, 22.8 MB) per step on the host cores"
+    return {
+        "impl": "reference", "metric": "w4a16_linear_hbm_gbs_m1", "value": round(value, 3), "unit": "GB/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms_per_step, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 (torch CPU)", "data": "synthetic (seeded N(0,0.02) weights, N(0,1) activations)",
+        "config": {"workload": "tinyllama_decode_linears_m1", "M": 1, "group_size": GROUP, "sample": sample},
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--impl", choices=["product", "reference"], default="product")
+    parser.add_argument("--pdl", action="store_true", help="launch the fused kernel with programmatic stream serialisation")
+    parser.add_argument("--quick", action="store_true", help="skip the per-shape tables")
+    args = parser.parse_args()
+    result = run_reference(args) if args.impl == "reference" else run_product(args)
+    if result:
+        print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()

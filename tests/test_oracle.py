@@ -148,3 +148,16 @@ def _assert_within_one_half_ulp_step(mine: np.ndarray, theirs: np.ndarray) -> No
     steps = np.abs(a - b)
     assert steps.max(initial=0) <= 1, f"max FP16 step distance {steps.max()}"
     assert (steps > 0).mean() < 0.02
+
+
+def test_torch_port_matches_numpy_oracle(golden):
+    """The torch restatement that the benchmark times on the host cores computes the same thing."""
+    import torch
+
+    from oracle import torch_cpu_port as port
+
+    data = golden("all_nibbles.npz")
+    packed, scales, x = (torch.from_numpy(data[key]) for key in ("packed", "scales", "x"))
+    assert np.array_equal(port.unpack_codes(packed).numpy(), data["codes"])
+    assert np.array_equal(port.dequantize(packed, scales, 128).numpy().view(np.uint32), data["dequant"].view(np.uint32))
+    _assert_within_one_half_ulp_step(port.linear(x, packed, scales, 128).numpy(), data["y"])
