@@ -49,15 +49,20 @@ enum {
      * that may still be running writes `packed` or `scales`. */
     W4A16_FLAG_PROGRAMMATIC_LAUNCH = 1u << 0,
     /* Route to the generic kernel even when the fast path applies (testing / A-B). */
-    W4A16_FLAG_FORCE_GENERIC = 1u << 1
+    W4A16_FLAG_FORCE_GENERIC = 1u << 1,
+    /* y is float [M, N] and receives the unrounded FP32 sums: for K-sharded layers whose partial
+     * results are added across devices before the single rounding to FP16. */
+    W4A16_FLAG_OUTPUT_F32 = 1u << 2
 };
 
 /* Explicit launch shape of the fused tensor-core kernel; zero fields mean "choose for me". */
 typedef struct w4a16_linear_config {
-    int32_t row_tiles;   /* 16-row tiles owned by one warp: 1, 2 or 4                             */
-    int32_t k_warps;     /* warps of a CTA that split K between them: 4 or 8                       */
-    int32_t k_splits;    /* CTAs that split K of one row block (>1 needs the workspace)            */
-    int32_t unroll;      /* 128-wide K chunks fetched per warp per pipeline step: 1, 2 or 4        */
+    int32_t row_tiles;   /* 16-row tiles owned by one warp: 1 or 2                                 */
+    int32_t k_warps;     /* warps of a CTA that split K of one row tile between them: 1, 2, 4, 8   */
+    int32_t k_splits;    /* CTAs that split K of one row tile: 1..8 (>1 needs the workspace)       */
+    int32_t unroll;      /* 128-wide K chunks per pipeline step: 1 or 2 (2 needs K/128 even and    */
+                         /* 4-byte aligned scales)                                                 */
+    int32_t stages;      /* slots of the asynchronous-copy ring each thread keeps in flight: 3..8  */
 } w4a16_linear_config;
 
 /*

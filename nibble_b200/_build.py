@@ -7,7 +7,7 @@ Two shared objects are produced next to this file:
 * ``_C.so`` -- the torch operator shim (``csrc/int4_linear.cpp``) that registers
   ``torch.ops.w4a16.linear`` / ``dequantize`` and forwards to the C ABI.
 
-``python -m nibble_b200._build`` builds both; nothing is rebuilt while the outputs are newer than
+``python nibble_b200/_build.py`` builds both; nothing is rebuilt while the outputs are newer than
 every source.
 """
 from __future__ import annotations

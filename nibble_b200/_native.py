@@ -24,6 +24,7 @@ class LinearConfig(ctypes.Structure):
         ("k_warps", ctypes.c_int32),
         ("k_splits", ctypes.c_int32),
         ("unroll", ctypes.c_int32),
+        ("stages", ctypes.c_int32),
     ]
 
 
@@ -52,7 +53,7 @@ FLAG_FORCE_GENERIC = 1 << 1
 def core() -> ctypes.CDLL:
     if not CORE_LIB.exists():
         raise RuntimeError(
-            f"{CORE_LIB.name} is not built; run `python -m nibble_b200._build` (needs nvcc)"
+            f"{CORE_LIB.name} is not built; run `python nibble_b200/_build.py` (needs nvcc)"
         )
     lib = ctypes.CDLL(str(CORE_LIB))
     for name, (restype, argtypes) in C_API.items():
@@ -69,7 +70,7 @@ def status_string(status: int) -> str:
 @functools.lru_cache(maxsize=None)
 def load_torch_ops() -> None:
     if not TORCH_LIB.exists():
-        raise ImportError(f"{TORCH_LIB.name} is not built; run `python -m nibble_b200._build`")
+        raise ImportError(f"{TORCH_LIB.name} is not built; run `python nibble_b200/_build.py`")
     import torch
 
     torch.ops.load_library(str(TORCH_LIB))

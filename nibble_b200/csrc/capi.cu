@@ -63,16 +63,18 @@ int w4a16_linear_f16(const void* x, const void* packed, const void* scales, void
     const int status = validate_linear(x, packed, scales, y, M, N, K, group_size);
     if (status != W4A16_OK || M == 0 || N == 0) return status;
     w4a16::LinearProblem p{static_cast<const __half*>(x), static_cast<const uint8_t*>(packed),
-                           static_cast<const __half*>(scales), static_cast<__half*>(y), M, N, K, group_size,
+                           static_cast<const __half*>(scales), y, M, N, K, group_size,
                            workspace, workspace_bytes};
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const bool out_f32 = (flags & W4A16_FLAG_OUTPUT_F32) != 0;
     if (K == 0) {
-        return cudaMemsetAsync(y, 0, static_cast<size_t>(M) * N * sizeof(__half), s) == cudaSuccess
+        const size_t element = out_f32 ? sizeof(float) : sizeof(__half);
+        return cudaMemsetAsync(y, 0, static_cast<size_t>(M) * N * element, s) == cudaSuccess
                    ? W4A16_OK
                    : W4A16_ERR_LAUNCH;
     }
     if ((flags & W4A16_FLAG_FORCE_GENERIC) || !fast_path_applies(x, packed, K, group_size)) {
-        return w4a16::launch_linear_generic(p, s);
+        return w4a16::launch_linear_generic(p, out_f32, s);
     }
     // Split K across CTAs only as far as the caller's workspace allows.
     int max_splits = 1;
@@ -84,8 +86,14 @@ int w4a16_linear_f16(const void* x, const void* packed, const void* scales, void
             }
         }
     }
-    const w4a16_linear_config cfg = w4a16::choose_linear_config(M, N, K, max_splits);
-    return w4a16::launch_linear_mma(p, cfg, (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0, s);
+    w4a16_linear_config cfg = w4a16::choose_linear_config(M, N, K, max_splits);
+    if (reinterpret_cast<uintptr_t>(scales) % 4 != 0) cfg.unroll = 1;
+    const int launched =
+        w4a16::launch_linear_mma(p, cfg, (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0, out_f32, s);
+    // Too much activation data for one CTA's shared memory and no workspace to split K further:
+    // the generic kernel has no such limit.
+    if (launched == W4A16_ERR_WORKSPACE) return w4a16::launch_linear_generic(p, out_f32, s);
+    return launched;
 }
 
 int w4a16_linear_f16_config(const void* x, const void* packed, const void* scales, void* y, int64_t M,
@@ -101,11 +109,12 @@ int w4a16_linear_f16_config(const void* x, const void* packed, const void* scale
     if (config->k_warps) cfg.k_warps = config->k_warps;
     if (config->k_splits) cfg.k_splits = config->k_splits;
     if (config->unroll) cfg.unroll = config->unroll;
+    if (config->stages) cfg.stages = config->stages;
     w4a16::LinearProblem p{static_cast<const __half*>(x), static_cast<const uint8_t*>(packed),
-                           static_cast<const __half*>(scales), static_cast<__half*>(y), M, N, K, group_size,
+                           static_cast<const __half*>(scales), y, M, N, K, group_size,
                            workspace, workspace_bytes};
     return w4a16::launch_linear_mma(p, cfg, (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0,
-                                    reinterpret_cast<cudaStream_t>(stream));
+                                    (flags & W4A16_FLAG_OUTPUT_F32) != 0, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int w4a16_dequantize_f16(const void* packed, const void* scales, void* weights, int64_t N, int64_t K,

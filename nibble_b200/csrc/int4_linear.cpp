@@ -60,8 +60,8 @@ void check_status(int status, const char* what) {
     TORCH_CHECK(status == W4A16_OK, what, " failed: ", w4a16_status_string(status));
 }
 
-at::Tensor linear_cuda_impl(const at::Tensor& activations, const at::Tensor& packed_weights,
-                            const at::Tensor& scales, int64_t group_size) {
+at::Tensor linear_impl(const at::Tensor& activations, const at::Tensor& packed_weights, const at::Tensor& scales,
+                       int64_t group_size, bool out_f32) {
     TORCH_CHECK(activations.is_cuda(), "activations must be a CUDA tensor");
     TORCH_CHECK(packed_weights.is_cuda(), "packed_weights must be a CUDA tensor");
     TORCH_CHECK(scales.is_cuda(), "scales must be a CUDA tensor");
@@ -88,11 +88,11 @@ at::Tensor linear_cuda_impl(const at::Tensor& activations, const at::Tensor& pac
                 "scales must have shape [N, K / group_size]");
 
     const c10::cuda::CUDAGuard guard(activations.device());
-    at::Tensor output = at::empty({m, n}, activations.options());
+    at::Tensor output = at::empty({m, n}, out_f32 ? activations.options().dtype(at::kFloat) : activations.options());
     if (m == 0 || n == 0) return output;
 
     const cudaStream_t stream = at::cuda::getCurrentCUDAStream().stream();
-    const uint32_t flags = flags_from_env();
+    const uint32_t flags = flags_from_env() | (out_f32 ? W4A16_FLAG_OUTPUT_F32 : 0u);
     const int forced_tiles = row_tiles_from_env();
 
     void* workspace = nullptr;
@@ -108,7 +108,7 @@ at::Tensor linear_cuda_impl(const at::Tensor& activations, const at::Tensor& pac
     if (forced_tiles != 0 && !(flags & W4A16_FLAG_FORCE_GENERIC) && group_size == 128 &&
         reinterpret_cast<uintptr_t>(activations.data_ptr()) % 16 == 0 &&
         reinterpret_cast<uintptr_t>(packed_weights.data_ptr()) % 16 == 0) {
-        w4a16_linear_config config = {forced_tiles, 0, 0, 0};
+        w4a16_linear_config config = {forced_tiles, 0, 0, 0, 0};
         status = w4a16_linear_f16_config(activations.data_ptr(), packed_weights.data_ptr(), scales.data_ptr(),
                                          output.data_ptr(), m, n, k, group_size, workspace, workspace_bytes,
                                          flags, &config, reinterpret_cast<w4a16_stream_t>(stream));
@@ -119,6 +119,17 @@ at::Tensor linear_cuda_impl(const at::Tensor& activations, const at::Tensor& pac
     }
     check_status(status, "w4a16::linear");
     return output;
+}
+
+at::Tensor linear_cuda_impl(const at::Tensor& activations, const at::Tensor& packed_weights,
+                            const at::Tensor& scales, int64_t group_size) {
+    return linear_impl(activations, packed_weights, scales, group_size, false);
+}
+
+// Same product with the unrounded FP32 sums as output: the per-device partial of a K-sharded layer.
+at::Tensor linear_partial_cuda_impl(const at::Tensor& activations, const at::Tensor& packed_weights,
+                                    const at::Tensor& scales, int64_t group_size) {
+    return linear_impl(activations, packed_weights, scales, group_size, true);
 }
 
 at::Tensor dequantize_cuda_impl(const at::Tensor& packed_weights, const at::Tensor& scales, int64_t group_size) {
@@ -158,9 +169,12 @@ at::Tensor dequantize_cuda_impl(const at::Tensor& packed_weights, const at::Tens
 TORCH_LIBRARY(w4a16, m) {
     m.def("linear(Tensor activations, Tensor packed_weights, Tensor scales, int group_size) -> Tensor");
     m.def("dequantize(Tensor packed_weights, Tensor scales, int group_size) -> Tensor");
+    // not in the reference: FP32 partial sums for layers sharded along K
+    m.def("linear_partial(Tensor activations, Tensor packed_weights, Tensor scales, int group_size) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(w4a16, CUDA, m) {
     m.impl("linear", &linear_cuda_impl);
     m.impl("dequantize", &dequantize_cuda_impl);
+    m.impl("linear_partial", &linear_partial_cuda_impl);
 }

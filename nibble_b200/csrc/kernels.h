@@ -23,7 +23,7 @@ struct LinearProblem {
     const __half* x;          // [M, K]
     const uint8_t* packed;    // [N, K/2]
     const __half* scales;     // [N, K/group]
-    __half* y;                // [M, N]
+    void* y;                  // [M, N], FP16 or FP32
     int64_t M, N, K, group;
     void* workspace;          // may be null
     size_t workspace_bytes;
@@ -37,11 +37,12 @@ size_t linear_workspace_bytes_for(int64_t M, int64_t N, int splits);
 w4a16_linear_config choose_linear_config(int64_t M, int64_t N, int64_t K, int max_splits);
 
 // Tensor-core path: requires group == 128 and 16-byte aligned x / packed.  Returns a W4A16_* code.
+// `out_f32` makes y an FP32 [M, N] matrix (unrounded sums, for partial results that are added up).
 int launch_linear_mma(const LinearProblem& p, const w4a16_linear_config& cfg, bool programmatic,
-                      cudaStream_t stream);
+                      bool out_f32, cudaStream_t stream);
 
 // Any even group size, any alignment, any M.
-int launch_linear_generic(const LinearProblem& p, cudaStream_t stream);
+int launch_linear_generic(const LinearProblem& p, bool out_f32, cudaStream_t stream);
 
 int launch_dequantize(const uint8_t* packed, const __half* scales, __half* weights, int64_t N,
                       int64_t K, int64_t group, cudaStream_t stream);

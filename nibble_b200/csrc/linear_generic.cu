@@ -17,8 +17,8 @@ constexpr int kGenericWarps = 4;
 
 __global__ void __launch_bounds__(kGenericWarps * 32)
 linear_generic_kernel(const __half* __restrict__ x, const uint8_t* __restrict__ packed,
-                      const __half* __restrict__ scales, __half* __restrict__ y, int64_t M, int64_t N,
-                      int64_t K, int64_t group) {
+                      const __half* __restrict__ scales, void* __restrict__ y, int64_t M, int64_t N,
+                      int64_t K, int64_t group, int out_f32) {
     const int lane = threadIdx.x & 31;
     const int64_t row = static_cast<int64_t>(blockIdx.x) * kGenericWarps + (threadIdx.x >> 5);
     if (row >= N) return;
@@ -52,19 +52,25 @@ linear_generic_kernel(const __half* __restrict__ x, const uint8_t* __restrict__ 
         float v = total[m];
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-        if (lane == 0 && m0 + m < M) y[(m0 + m) * N + row] = __float2half_rn(v);
+        if (lane == 0 && m0 + m < M) {
+            if (out_f32) {
+                static_cast<float*>(y)[(m0 + m) * N + row] = v;
+            } else {
+                static_cast<__half*>(y)[(m0 + m) * N + row] = __float2half_rn(v);
+            }
+        }
     }
 }
 
 }  // namespace
 
-int launch_linear_generic(const LinearProblem& p, cudaStream_t stream) {
+int launch_linear_generic(const LinearProblem& p, bool out_f32, cudaStream_t stream) {
     const int64_t row_blocks = (p.N + kGenericWarps - 1) / kGenericWarps;
     const int64_t batch_blocks = (p.M + kGenericBatch - 1) / kGenericBatch;
     if (row_blocks > INT32_MAX || batch_blocks > 65535) return W4A16_ERR_TOO_LARGE;
     const dim3 grid(static_cast<unsigned>(row_blocks), static_cast<unsigned>(batch_blocks), 1);
     linear_generic_kernel<<<grid, kGenericWarps * 32, 0, stream>>>(p.x, p.packed, p.scales, p.y, p.M, p.N,
-                                                                   p.K, p.group);
+                                                                   p.K, p.group, out_f32 ? 1 : 0);
     if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return W4A16_OK;

@@ -105,6 +105,17 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// D = A * B + C with C read from caller-kept registers (e.g. four that stay zero) and D written
+// elsewhere: lets the first MMA of a sum skip clearing its accumulator.
+__device__ __forceinline__ void mma_m16n8k16_from(float (&d)[4], const float (&c)[4], uint32_t a0, uint32_t a1,
+                                                  uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+        "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
 // Programmatic dependent launch.  Both are no-ops for a kernel launched the ordinary way.
 __device__ __forceinline__ void pdl_wait_for_upstream() {
     asm volatile("griddepcontrol.wait;" ::: "memory");

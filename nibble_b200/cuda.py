@@ -11,20 +11,17 @@ import torch
 
 from . import _native
 
-try:
-    _native.load_torch_ops()
-except (ImportError, OSError) as error:  # not built, or built against another torch
-    _EXTENSION_LOAD_ERROR: Exception | None = error
-else:
-    _EXTENSION_LOAD_ERROR = None
-
-
-if _EXTENSION_LOAD_ERROR is None:
+def _register_fakes() -> None:
+    """Shape-only kernels so ``torch.compile`` can trace through the native operators."""
 
     @torch.library.register_fake("w4a16::linear")
     def _linear_fake(activations, packed_weights, scales, group_size):
         # [M, K] x [N, K/2] -> [M, N], dtype of the activations
         return activations.new_empty((activations.shape[0], packed_weights.shape[0]))
+
+    @torch.library.register_fake("w4a16::linear_partial")
+    def _linear_partial_fake(activations, packed_weights, scales, group_size):
+        return activations.new_empty((activations.shape[0], packed_weights.shape[0]), dtype=torch.float32)
 
     @torch.library.register_fake("w4a16::dequantize")
     def _dequantize_fake(packed_weights, scales, group_size):
@@ -32,6 +29,15 @@ if _EXTENSION_LOAD_ERROR is None:
         return packed_weights.new_empty(
             (packed_weights.shape[0], packed_weights.shape[1] * 2), dtype=torch.float16
         )
+
+
+try:
+    _native.load_torch_ops()
+    _register_fakes()
+except (ImportError, OSError, RuntimeError) as error:  # not built, stale, or built against another torch
+    _EXTENSION_LOAD_ERROR: Exception | None = error
+else:
+    _EXTENSION_LOAD_ERROR = None
 
 
 def cuda_extension_available() -> bool:
@@ -42,7 +48,7 @@ def cuda_extension_available() -> bool:
 def _require_extension() -> None:
     if _EXTENSION_LOAD_ERROR is not None:
         raise RuntimeError(
-            "The W4A16 CUDA extension is not built. Build it with `python -m nibble_b200._build`."
+            "The W4A16 CUDA extension is not built. Build it with `python nibble_b200/_build.py`."
         ) from _EXTENSION_LOAD_ERROR
 
 
@@ -73,3 +79,18 @@ def dequantize_cuda(
     """
     _require_extension()
     return torch.ops.w4a16.dequantize(packed_weights, scales, group_size)
+
+
+def linear_partial_cuda(
+    activations: torch.Tensor,
+    packed_weights: torch.Tensor,
+    scales: torch.Tensor,
+    group_size: int = 128,
+) -> torch.Tensor:
+    """``linear_cuda`` without the final rounding: FP32 ``[M, N]`` sums.
+
+    Not part of the reference's surface; used for layers sharded along K, whose per-device partial
+    results are added across devices before the single rounding to FP16.
+    """
+    _require_extension()
+    return torch.ops.w4a16.linear_partial(activations, packed_weights, scales, group_size)

@@ -57,7 +57,7 @@ def test_argument_validation_happens_before_any_launch():
     assert d(ctypes.c_void_p(8), one, one, 8, 128, 128, None) == -4  # packed not 16-byte aligned
     assert d(None, one, one, 8, 128, 128, None) == -1
     assert d(None, None, None, 0, 128, 128, None) == 0
-    cfg = _native.LinearConfig(1, 8, 1, 1)
+    cfg = _native.LinearConfig(1, 8, 1, 1, 0)
     g = lib.w4a16_linear_f16_config
     assert g(one, one, one, one, 1, 8, 128, 64, None, 0, 0, ctypes.byref(cfg), None) == -6  # fast path n/a
     assert g(one, one, one, one, 1, 8, 128, 128, None, 0, 0, None, None) == -1

@@ -80,18 +80,32 @@ def test_ragged_shapes(m, k, n):
     check_against_oracle(capi_linear(x, packed, scales), x, packed, scales)
 
 
-@pytest.mark.parametrize("m", [1, 8])
+@pytest.mark.parametrize("m", [1, 8, 20])
 @pytest.mark.parametrize("row_tiles", [1, 2])
-@pytest.mark.parametrize("k_warps", [4, 8])
+@pytest.mark.parametrize("k_warps", [1, 2, 4, 8])
 @pytest.mark.parametrize("k_splits", [1, 2, 3, 8])
-@pytest.mark.parametrize("unroll", [1, 2])
-def test_every_launch_shape(m, row_tiles, k_warps, k_splits, unroll):
-    k, n = 5632, 77   # 44 chunks: not a multiple of any k_warps * unroll * k_splits used here
+@pytest.mark.parametrize(("unroll", "stages"), [(1, 0), (1, 2), (1, 5), (2, 0), (2, 3), (2, 8)])
+def test_every_launch_shape(m, row_tiles, k_warps, k_splits, unroll, stages):
+    k, n = 5632, 77   # 44 chunks: ragged against most k_warps * unroll * k_splits combinations
     x, packed, scales = _random_case(m, k, n, seed=3)
     ws = new_workspace(m, n, k)
-    y = capi_linear(x, packed, scales, workspace=ws, config=(row_tiles, k_warps, k_splits, unroll))
-    check_against_oracle(y, x, packed, scales)
-    assert int(ws[:256].sum()) == 0, "arrival counters must be back at zero"
+    per_split = -(-(-(-44 // k_splits)) // unroll) * unroll
+    buildable = not (m > 16 and row_tiles == 2)          # 32-row batches come with one row tile only
+    valid = buildable and (k_splits - 1) * per_split < 44  # no K split may be empty
+    if stages and stages < 3:
+        valid = False
+    # the activation slice of a CTA plus a minimal copy ring must fit in shared memory
+    batch = min(m, 32)
+    nt = 1 if m <= 8 else (2 if m <= 16 else 4)
+    stage_bytes = 256 * (2 * row_tiles * unroll * 16 + (8 * row_tiles if unroll == 2 else 0))
+    red_bytes = 0 if k_warps == 1 else 2 * 8 * row_tiles * nt * 4 * 32 * 4
+    fits = batch * per_split * 256 + red_bytes + max(stages, 3) * stage_bytes <= 220 * 1024
+    y = capi_linear(x, packed, scales, workspace=ws, config=(row_tiles, k_warps, k_splits, unroll, stages),
+                    expect=(0 if fits else -5) if valid else -6)
+    valid = valid and fits
+    if valid:
+        check_against_oracle(y, x, packed, scales)
+        assert int(ws[:256].sum()) == 0, "arrival counters must be back at zero"
 
 
 def test_split_k_workspace_is_reusable_and_deterministic():
@@ -99,12 +113,12 @@ def test_split_k_workspace_is_reusable_and_deterministic():
     ws = new_workspace(4, 1024, 8192)
     first = capi_linear(x, packed, scales, workspace=ws)
     second = capi_linear(x, packed, scales, workspace=ws)
-    third = capi_linear(x, packed, scales, workspace=ws, config=(1, 8, 4, 2))
+    third = capi_linear(x, packed, scales, workspace=ws, config=(1, 8, 4, 2, 0))
     assert torch.equal(first, second)
     check_against_oracle(first, x, packed, scales)
     check_against_oracle(third, x, packed, scales)
     too_small = torch.zeros(1024, dtype=torch.uint8, device="cuda")
-    capi_linear(x, packed, scales, workspace=too_small, config=(1, 8, 4, 2), expect=-5)
+    capi_linear(x, packed, scales, workspace=too_small, config=(1, 8, 4, 2, 0), expect=-5)
     # without a workspace the library simply does not split
     check_against_oracle(capi_linear(x, packed, scales), x, packed, scales)
 
