@@ -246,6 +246,112 @@ def cpu_pass(torch, layers, sample_name: str, repeats: int) -> dict:
             "kind": "port", "sample": sample_name, "seconds_per_sample": round(seconds, 4)}
 
 
+def decode_bench(torch, device) -> dict:
+    """Decode tokens/s of a TinyLlama-1.1B-shaped model (random weights), FP16 cuBLAS vs W4A16.
+
+    Protocol of the reference's scripts/generate.py:307-365: batch 1, 16-token prompt of seeded
+    random ids, 32 greedy new tokens, static KV cache, the decode step replayed from a CUDA graph;
+    decode tok/s = (new - 1) / (total - prefill); one warm-up, median of five.  No tokenizer and no
+    checkpoint are involved (neither is available offline): the architecture and sizes are real,
+    the weights are random, so only speed -- not text -- is meaningful.
+    """
+    import transformers
+    from transformers import StaticCache
+
+    from nibble_b200 import replace_linear_layers
+
+    cfg = transformers.LlamaConfig(
+        vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hidden_layers=22,
+        num_attention_heads=32, num_key_value_heads=4, max_position_embeddings=2048, rms_norm_eps=1e-5,
+        tie_word_embeddings=False,
+    )
+    torch.manual_seed(0)
+    with torch.device(device):
+        model = transformers.AutoModelForCausalLM.from_config(cfg, dtype=torch.float16)
+    model.eval()
+    prompt_len, new_tokens = 16, 32
+    prompt = torch.randint(0, 32000, (1, prompt_len), generator=torch.Generator().manual_seed(0)).to(device)
+    positions = torch.arange(prompt_len, device=device)
+
+    def measure(label: str) -> dict:
+        cache = StaticCache(config=cfg, max_cache_len=prompt_len + new_tokens + 8)
+        tok = torch.zeros((1, 1), dtype=torch.long, device=device)
+        pos = torch.zeros((1,), dtype=torch.long, device=device)
+
+        def prefill():
+            cache.reset()
+            out = model(input_ids=prompt, past_key_values=cache, cache_position=positions, use_cache=True)
+            return out.logits[:, -1].argmax(-1, keepdim=True)
+
+        def step():
+            out = model(input_ids=tok, past_key_values=cache, cache_position=pos, use_cache=True)
+            return out.logits[:, -1].argmax(-1, keepdim=True)
+
+        with torch.inference_mode():
+            tok.copy_(prefill())
+            pos.fill_(prompt_len)
+            for _ in range(3):   # lazy cache allocation, workspace allocation, autotuning
+                step()
+            torch.cuda.synchronize()
+            mode = "cuda_graph"
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    next_tok = step()
+                replay = graph.replay
+            except Exception as error:   # a host sync inside the model: time eager launches instead
+                torch.cuda.synchronize()
+                mode = f"eager ({type(error).__name__})"
+                holder = [None]
+
+                def replay():
+                    holder[0] = step()
+
+                replay()
+                next_tok = holder[0]
+
+            def generate():
+                e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                e0.record()
+                first = prefill()
+                e1.record()
+                tok.copy_(first)
+                pos.fill_(prompt_len)
+                for _ in range(new_tokens - 1):
+                    replay()
+                    tok.copy_(next_tok if mode == "cuda_graph" else holder[0])
+                    pos.add_(1)
+                e2.record()
+                torch.cuda.synchronize()
+                return e0.elapsed_time(e1), e0.elapsed_time(e2)
+
+            generate()
+            runs = [generate() for _ in range(5)]
+        prefill_ms = statistics.median(r[0] for r in runs)
+        total_ms = statistics.median(r[1] for r in runs)
+        decode_ms = total_ms - prefill_ms
+        row = {"decode_tok_s": round((new_tokens - 1) / decode_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
+               "ms_per_token": round(decode_ms / (new_tokens - 1), 4), "e2e_tok_s": round(new_tokens / total_ms * 1e3, 1),
+               "mode": mode, "peak_mib": round(torch.cuda.max_memory_allocated(device) / 2**20)}
+        log(f"  decode {label}: {row}")
+        return row
+
+    out = {"model": "TinyLlama-1.1B architecture, random weights", "prompt_tokens": prompt_len, "new_tokens": new_tokens}
+    torch.cuda.reset_peak_memory_stats(device)
+    out["fp16_cublas"] = measure("fp16")
+    replaced = replace_linear_layers(model, group_size=GROUP)
+    out["linears_replaced"] = replaced
+    torch.cuda.empty_cache()
+    torch.cuda.reset_peak_memory_stats(device)
+    out["w4a16"] = measure("w4a16")
+    os.environ["W4A16_PDL"] = "1"
+    out["w4a16_programmatic_launch"] = measure("w4a16+pdl")
+    os.environ.pop("W4A16_PDL", None)
+    del model
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_product(args) -> dict:
     import torch
     import torch.distributed as dist
@@ -394,6 +500,12 @@ def run_product(args) -> dict:
             "llama70b_m1": per_shape_table(torch, LLAMA70B, 1, device, l2, with_cublas=False),
             "llama70b_m8": per_shape_table(torch, LLAMA70B, 8, device, l2, with_cublas=True),
         }
+    if rank == 0 and world == 1 and not args.quick:
+        log("decode tokens/s, TinyLlama-1.1B-shaped model")
+        try:
+            result["decode"] = decode_bench(torch, device)
+        except Exception as error:   # transformers API drift must not cost the headline line
+            result["decode"] = {"error": repr(error)[:300]}
     if rank == 0 and world == 1:
         block = [(name, *TINYLLAMA[name]) for name in BLOCK_ORDER]
         result["cpu_baseline"] = cpu_pass(torch, block * 4, "4 decoder blocks (28 linears) of the workload, M=1", repeats=5)

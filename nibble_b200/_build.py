@@ -29,7 +29,7 @@ TORCH_LIB = PKG / "_C.so"
 CUDA_SOURCES = ["capi.cu", "linear_mma.cu", "linear_generic.cu", "dequantize.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-O3", "-std=c++17", "-lineinfo",
+    "-O3", "-std=c++20", "-lineinfo",
     "-Xcompiler", "-fPIC",
     "-Xptxas", "-v",
 ]

@@ -1,7 +1,7 @@
-// Fused W4A16 linear for sm_100a: packed INT4 weights are streamed from HBM straight into
-// registers, unpacked to exact FP16 integers with two-instruction-per-pair bit tricks, and fed to
-// the tensor cores as the 16-row operand of m16n8k16 MMAs whose 8-wide axis carries the batch.
-// The group scale multiplies the FP32 accumulator once per 128 k, never the individual weights.
+// Fused W4A16 linear for sm_100a: packed INT4 weights are streamed from HBM, unpacked to exact FP16
+// integers with two-instruction-per-pair bit tricks, and fed to the tensor cores as the 16-row
+// operand of m16n8k16 MMAs whose 8-wide axis carries the batch.  The group scale multiplies the
+// FP32 accumulator once per 128 k, never the individual weights.
 //
 // Replaces the reference's M=1 decode kernel (csrc/int4_linear_kernel.cu:325-404), its M=2..8
 // small-batch kernel (:542-617) and, for larger M, its dequantise-then-cuBLAS route
@@ -11,18 +11,27 @@
 // Shape of a launch
 //   CTA        : 8 warps = RW row groups x KW warps; the KW warps of a group split the K range of
 //                one row tile between them (contiguous sub-ranges), the RW groups own different
-//                row tiles.  CTAs are persistent: the grid is sized to what is resident at once
-//                and every group strides over the row tiles.
+//                row tiles.  CTAs are persistent: the grid is what is resident at once and every
+//                group strides over the row tiles.
 //   row tile   : 16*TILES consecutive output rows.  Row-major [N, K/2] makes a row's K range one
-//                contiguous byte run; lane (g, t) reads 16 bytes of rows g and g+8 per 128-wide K
-//                chunk with L1-bypassing loads, so a quad covers the 64 bytes of one scale group.
+//                contiguous byte run; lane (g, t) owns 16 bytes of rows g and g+8 per 128-wide K
+//                chunk, so a quad covers the 64 bytes of one scale group.
+//   weights    : each thread keeps a ring of STAGES slots in shared memory, filled with 16-byte
+//                cp.async copies of exactly the bytes its own MMAs will consume (plus one 4-byte
+//                scale pair per row).  The thread's own cp.async.wait_group is the only
+//                synchronisation of the stream, and the bytes in flight per SM are set by the ring
+//                depth, not by registers.  Slot addresses are compile-time offsets: the step loop
+//                is unrolled over the ring.
 //   x          : copied once per CTA into shared memory, already permuted to the (k, k+4) pairing
-//                the unpack produces and laid out so a warp's B-fragment read is one conflict-free
-//                512-byte row.
-//   scales     : U consecutive FP16 scales of a row in one 2*U-byte load.
+//                the unpack produces; a warp's B-fragment read is one conflict-free 512-byte row.
 //   reduction  : warps of a group combine through shared memory (one named barrier per group and
 //                tile); optional K-split CTAs (grid.y) combine through an FP32 workspace, the
 //                group that arrives last summing the partials in split order.
+//
+// The instruction budget is what bounds this kernel on B200: at 6.5 TB/s an SM has about 43 clocks
+// per KB of packed weights, lop3/shf/prmt and fma.f16x2 each issue at 2 warp-instructions per clock
+// per SM, and the unpack alone needs 40 + 32 of them per KB.  Hence no per-step address arithmetic,
+// no register clearing and no register-to-register copies in the step loop.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -39,8 +48,8 @@ namespace {
 constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = kWarpsPerCta * 32;
 constexpr int kSmemBudget = 220 * 1024;   // dynamic shared memory a CTA may ask for
+constexpr int kFlagBytes = 128;           // split-K arrival flags at the head of the dynamic shared memory
 constexpr int kSmemPerSm = 228 * 1024;    // shared memory of one SM; every resident CTA also reserves 1 KB
-constexpr int kMaxStages = 8;
 
 struct MmaParams {
     const __half* x;
@@ -55,7 +64,6 @@ struct MmaParams {
     int k_splits;
     int row_tiles_total;   // ceil(N / (16 * TILES))
     int out_f32;
-    int stages;            // slots of the per-thread copy ring (2..8)
 };
 
 __device__ __forceinline__ void group_barrier(int id, int threads) {
@@ -66,53 +74,48 @@ __device__ __forceinline__ unsigned smem_addr(const void* p) {
     return static_cast<unsigned>(__cvta_generic_to_shared(p));
 }
 
+template <int OFFSET>
 __device__ __forceinline__ uint4 lds16(unsigned addr) {
     uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr), "n"(OFFSET));
     return v;
 }
 
+template <int OFFSET>
 __device__ __forceinline__ uint32_t lds4(unsigned addr) {
     uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFFSET));
     return v;
 }
 
 // Asynchronous global -> shared copies (no register staging).  The 16-byte form bypasses L1.
+template <int DST_OFFSET, int SRC_OFFSET>
 __device__ __forceinline__ void cp_async16(unsigned dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    asm volatile("cp.async.cg.shared.global [%0+%1], [%2+%3], 16;" ::"r"(dst), "n"(DST_OFFSET), "l"(src),
+                 "n"(SRC_OFFSET)
+                 : "memory");
 }
+template <int DST_OFFSET, int SRC_OFFSET>
 __device__ __forceinline__ void cp_async4(unsigned dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+    asm volatile("cp.async.ca.shared.global [%0+%1], [%2+%3], 4;" ::"r"(dst), "n"(DST_OFFSET), "l"(src),
+                 "n"(SRC_OFFSET)
+                 : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 
-// Wait until at most `pending` of this thread's committed copy groups are still in flight.
-__device__ __forceinline__ void cp_async_wait(int pending) {
-    if (pending <= 0) {
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-    } else if (pending == 1) {
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else if (pending == 2) {
-        asm volatile("cp.async.wait_group 2;" ::: "memory");
-    } else if (pending == 3) {
-        asm volatile("cp.async.wait_group 3;" ::: "memory");
-    } else if (pending == 4) {
-        asm volatile("cp.async.wait_group 4;" ::: "memory");
-    } else if (pending == 5) {
-        asm volatile("cp.async.wait_group 5;" ::: "memory");
-    } else if (pending == 6) {
-        asm volatile("cp.async.wait_group 6;" ::: "memory");
-    } else {
-        asm volatile("cp.async.wait_group 7;" ::: "memory");
-    }
+// Wait until at most PENDING of this thread's committed copy groups are still in flight.
+template <int PENDING>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
 }
 
-// Bytes one pipeline stage occupies per CTA: every thread parks U chunks x 2*TILES rows x 16 bytes
-// of packed weights plus (U == 2) one 4-byte scale pair per row.
+// Bytes one pipeline stage occupies per CTA: per thread U chunks x 2*TILES rows x 16 bytes of
+// packed weights, plus (U == 2) per warp one 4-byte scale pair for each of its 16*TILES rows.
 template <int TILES, int U>
 __host__ __device__ constexpr int stage_bytes() {
-    return kThreads * (2 * TILES * U * 16 + (U == 2 ? 2 * TILES * 4 : 0));
+    return kThreads * (2 * TILES * U * 16) + (U == 2 ? kWarpsPerCta * 16 * TILES * 4 : 0);
 }
 
 // Resident CTAs per SM the register allocation aims for.
@@ -121,7 +124,11 @@ __host__ __device__ constexpr int min_ctas_per_sm() {
     return (NT * TILES <= 2) ? 2 : 1;
 }
 
-template <int NT, int TILES, int KW, int U>
+// NT     n8 tiles of the batch a CTA handles per pass (batch rows = up to 8*NT)
+// XB     batch rows stored per chunk in the shared copy of x: 1 (M == 1) or 8*NT (padded)
+// TILES  16-row tiles per warp           KW  warps splitting K of one row tile
+// U      chunks per pipeline step        STAGES  ring depth
+template <int NT, int XB, int TILES, int KW, int U, int STAGES>
 __global__ void __launch_bounds__(kThreads, min_ctas_per_sm<NT, TILES>())
 linear_mma_kernel(const MmaParams p) {
     constexpr int RW = kWarpsPerCta / KW;
@@ -131,16 +138,21 @@ linear_mma_kernel(const MmaParams p) {
     constexpr int kStageBytes = stage_bytes<TILES, U>();
     constexpr int kItemBytes = kThreads * 16;                            // one 16-byte item of every thread
     constexpr int kScaleOffset = 2 * TILES * U * kItemBytes;             // scales follow the weights
+    constexpr int kPeriod = (STAGES % 2 == 0) ? STAGES : 2 * STAGES;     // steps per unrolled loop body
+    static_assert(STAGES >= 3, "the step loop prefetches one slot ahead of the one it computes on");
 
-    extern __shared__ __align__(16) unsigned char smem[];
-    float* red_all = reinterpret_cast<float*>(smem);
-    const unsigned ring = smem_addr(smem + sizeof(float) * kRedFloats * RW);
-    const unsigned ring_end = ring + static_cast<unsigned>(p.stages) * kStageBytes;
-    const unsigned xs = ring_end;
-    __shared__ int last_flag[RW];
+    // All shared memory is dynamic and 128-byte aligned, and so is every region in it: a 16-byte
+    // cp.async whose destination straddles two 32-byte shared-memory sectors cannot be merged with
+    // its neighbour lane's and costs a second sector fetch from L2.
+    extern __shared__ __align__(128) unsigned char smem[];
+    int* last_flag = reinterpret_cast<int*>(smem);                      // [RW], first 128 bytes
+    float* red_all = reinterpret_cast<float*>(smem + kFlagBytes);
+    const unsigned ring = smem_addr(smem + kFlagBytes + sizeof(float) * kRedFloats * RW);
+    const unsigned xs = ring + STAGES * kStageBytes;
 
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
     const int group = warp / KW;          // which row tile of the CTA
     const int kw = warp % KW;             // which K sub-range of the tile
     const int g = lane >> 2;
@@ -163,84 +175,116 @@ linear_mma_kernel(const MmaParams p) {
 
     const int tile_stride = gridDim.x * RW;
     const int first_tile = blockIdx.x * RW + group;
+    int my_tiles = 0;
+    if (first_tile < p.row_tiles_total) my_tiles = (p.row_tiles_total - 1 - first_tile) / tile_stride + 1;
 
-    const int tid = threadIdx.x;
-
-    // ---- producer side: a private ring of `stages` slots per thread ---------------------------
-    // Each thread copies exactly the bytes it will later feed to its own MMAs, so completion of its
-    // own copy groups is the only synchronisation the weight stream needs.
-    const uint8_t* p_src[TILES][2];
-    const __half* p_scl[TILES][2];
+    // ---- producer side ------------------------------------------------------------------------
+    // U == 2: a step is 128 contiguous bytes of each of the warp's 16*TILES rows.  Copy j of a lane
+    // moves piece (lane & 7) of row 4j + lane/8, so every warp-wide cp.async covers four whole
+    // 128-byte lines; the bytes land where the lane that will consume them expects them
+    // (item (chunk, row half), entry row%8 * 4 + piece%4).  The warp therefore shares its slots:
+    // one __syncwarp after the wait publishes them, and orders the refill after everyone's reads.
+    // U == 1: a step is 64 bytes per row and every lane copies exactly what it consumes itself.
+    constexpr int kCopies = U == 2 ? 4 * TILES : 2 * TILES;   // 16-byte copies per lane per step
+    const unsigned ring_w = ring + tid * 16;                  // consumer view: this lane's entry of item 0
+    const unsigned ring_s = ring + kScaleOffset + warp * (16 * TILES * 4);   // this warp's scale pairs
+    const unsigned copy_dst = U == 2
+        ? ring + ((lane >> 2) & 1) * kItemBytes + (warp * 32 + (lane >> 3) * 4 + (lane & 3)) * 16
+        : ring_w;
+    // Source pointers are kept "as of position 0 of the unrolled period": the copy issued at
+    // position POS reads p_src + POS * (bytes per step), an immediate, so the pointers move once per
+    // period instead of once per step.
+    constexpr int kStepBytes = U * kChunkBytes;               // packed bytes of one row per step
+    const uint8_t* p_src[kCopies];
+    const __half* p_scl = nullptr;
     int p_tile = first_tile;
-    int p_left = 0;                                          // steps still to issue for p_tile
-    unsigned p_waddr = ring + tid * 16;                      // this thread's first weight item of the slot
-    unsigned p_saddr = ring + kScaleOffset + tid * 4;        // this thread's first scale pair of the slot
-    const unsigned ring_bytes = static_cast<unsigned>(p.stages) * kStageBytes;
-    auto point_producer_at = [&](int tile_index) {
+    int p_left = 0;                                           // steps still to issue for p_tile
+    const bool scale_lane = lane < 16 * TILES;
+    auto point_producer_at = [&](int tile_index, int pos) {
         const int row0 = tile_index * kRowsPerTile;
 #pragma unroll
-        for (int tl = 0; tl < TILES; ++tl) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int r = min(row0 + tl * 16 + h * 8 + g, p.N - 1);   // rows past N: load the last row
-                p_src[tl][h] = p.packed + static_cast<size_t>(r) * row_bytes +
-                               static_cast<size_t>(w_begin) * kChunkBytes + t * 16;
-                p_scl[tl][h] = p.scales + static_cast<size_t>(r) * p.chunks + w_begin;
-            }
+        for (int j = 0; j < kCopies; ++j) {
+            // rows past N re-read the last row; their results are never stored
+            const int local = U == 2 ? 4 * j + (lane >> 3) : 8 * j + g;
+            const int piece = U == 2 ? (lane & 7) : t;
+            const int r = min(row0 + local, p.N - 1);
+            p_src[j] = p.packed + static_cast<size_t>(r) * row_bytes + static_cast<size_t>(w_begin) * kChunkBytes +
+                       piece * 16 - pos * kStepBytes;
+        }
+        if constexpr (U == 2) {
+            const int r = min(row0 + (lane & (16 * TILES - 1)), p.N - 1);
+            p_scl = p.scales + static_cast<size_t>(r) * p.chunks + w_begin - pos * U;
         }
         p_left = steps_per_tile;
     };
-    if (steps_per_tile > 0 && p_tile < p.row_tiles_total) point_producer_at(p_tile);
+    if (steps_per_tile > 0 && my_tiles > 0) point_producer_at(p_tile, 0);
 
-    auto issue_step = [&]() {
+    auto copy_at = [&](auto pos_tag, auto j_tag) {
+        constexpr int POS = decltype(pos_tag)::value;
+        constexpr int SLOT = POS % STAGES;
+        constexpr int j = decltype(j_tag)::value;
+        if constexpr (j < kCopies) {
+            // U == 2: copy j -> tile j/4, row half (j/2)%2, rows (j%2)*4 .. +3 of that half
+            constexpr int OFFSET = U == 2
+                ? SLOT * kStageBytes + ((j >> 2) * 2 + ((j >> 1) & 1)) * U * kItemBytes + (j & 1) * 256
+                : SLOT * kStageBytes + j * kItemBytes;
+            cp_async16<OFFSET, POS * kStepBytes>(copy_dst, p_src[j]);
+        }
+    };
+    // Requests the next step of this warp's stream into the ring slot of period position POS and
+    // commits the group (an empty group when the stream is exhausted keeps group count and slot
+    // count in step).
+    auto issue_step = [&](auto pos_tag) {
+        constexpr int POS = decltype(pos_tag)::value;
+        constexpr int SLOT = POS % STAGES;
+        constexpr int NEXT_POS = (POS + 1) % kPeriod;
         if (p_left > 0) {
-#pragma unroll
-            for (int tl = 0; tl < TILES; ++tl) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        cp_async16(p_waddr + ((tl * 2 + h) * U + u) * kItemBytes, p_src[tl][h] + u * kChunkBytes);
-                    }
-                    if constexpr (U == 2) {
-                        cp_async4(p_saddr + (tl * 2 + h) * (kThreads * 4), p_scl[tl][h]);
-                        p_scl[tl][h] += U;
-                    }
-                    p_src[tl][h] += U * kChunkBytes;
-                }
+            copy_at(pos_tag, std::integral_constant<int, 0>{});
+            copy_at(pos_tag, std::integral_constant<int, 1>{});
+            copy_at(pos_tag, std::integral_constant<int, 2>{});
+            copy_at(pos_tag, std::integral_constant<int, 3>{});
+            copy_at(pos_tag, std::integral_constant<int, 4>{});
+            copy_at(pos_tag, std::integral_constant<int, 5>{});
+            copy_at(pos_tag, std::integral_constant<int, 6>{});
+            copy_at(pos_tag, std::integral_constant<int, 7>{});
+            if constexpr (U == 2) {
+                if (scale_lane) cp_async4<SLOT * kStageBytes, POS * U * 2>(ring_s + lane * 4, p_scl);
             }
             if (--p_left == 0) {
                 p_tile += tile_stride;
-                if (p_tile < p.row_tiles_total) point_producer_at(p_tile);
+                if (p_tile < p.row_tiles_total) point_producer_at(p_tile, NEXT_POS);
+            } else if constexpr (NEXT_POS == 0) {
+#pragma unroll
+                for (int j = 0; j < kCopies; ++j) p_src[j] += kPeriod * kStepBytes;
+                if constexpr (U == 2) p_scl += kPeriod * U;
             }
         }
-        cp_async_commit();   // an empty group keeps the group count in step with the slot count
-        p_waddr += kStageBytes;
-        p_saddr += kStageBytes;
-        if (p_waddr >= ring_end) {
-            p_waddr -= ring_bytes;
-            p_saddr -= ring_bytes;
-        }
+        cp_async_commit();
+    };
+    auto issue_all_slots = [&]<int... S>(std::integer_sequence<int, S...>) {
+        (issue_step(std::integral_constant<int, S>{}), ...);
     };
 
     // Weights and scales never depend on the previous kernel of the stream, so the whole ring is
     // requested before waiting for it; x and y may, so they are touched only after the wait.
-    for (int s = 0; s < p.stages; ++s) issue_step();
+    issue_all_slots(std::make_integer_sequence<int, STAGES>{});
     pdl_release_downstream();
     pdl_wait_for_upstream();
 
     // ---- stage this CTA's slice of x in shared memory, in B-fragment order --------------------
-    // 16-byte unit ((c * 4 + i) * batch_here + n) * 4 + t  holds, for batch row n, the eight
-    // activations k = c*128 + t*32 + i*8 .. +8 re-paired as (x0,x4)(x1,x5)(x2,x6)(x3,x7).
+    // 16-byte unit ((c * 4 + i) * XB + n) * 4 + t holds, for batch row n, the eight activations
+    // k = c*128 + t*32 + i*8 .. +8 re-paired as (x0,x4)(x1,x5)(x2,x6)(x3,x7).  Rows past the batch
+    // repeat its last row: their products land in output columns that are never stored.
     {
         const int units_per_row = span * 16;   // 16-byte pieces of one batch row in this K slice
-        for (int n = 0; n < batch_here; ++n) {
-            const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m0 + n) * p.K +
+        for (int n = 0; n < XB; ++n) {
+            const int src_row = m0 + min(n, batch_here - 1);
+            const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(src_row) * p.K +
                                                               static_cast<size_t>(c_begin) * kGroup);
             for (int j = tid; j < units_per_row; j += kThreads) {
                 const uint4 q = ldg_keep16(src + j);
                 const int c = j >> 4, tt = (j >> 2) & 3, i = j & 3;
-                const unsigned dst = xs + (((c * 4 + i) * batch_here + n) * 4 + tt) * 16;
+                const unsigned dst = xs + (((c * 4 + i) * XB + n) * 4 + tt) * 16;
                 asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(prmt(q.x, q.z, 0x5410u)),
                              "r"(prmt(q.x, q.z, 0x7632u)), "r"(prmt(q.y, q.w, 0x5410u)),
                              "r"(prmt(q.y, q.w, 0x7632u))
@@ -250,149 +294,159 @@ linear_mma_kernel(const MmaParams p) {
     }
     __syncthreads();
 
-    // B-fragment addressing: lane (g, t) reads unit (i * batch_here + n) * 4 + t of a chunk, n being
-    // its batch column nt*8 + g.  Columns past the batch re-read the last live row instead of being
-    // zero-filled: their products land in output columns that are never stored.
-    unsigned x_lane[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        const int n = min(nt * 8 + g, batch_here - 1);
-        x_lane[nt] = xs + static_cast<unsigned>(w_begin - c_begin) * batch_here * 256 + (n * 4 + t) * 16;
-    }
-    const unsigned x_i_stride = static_cast<unsigned>(batch_here) * 64;
-    const unsigned x_chunk_stride = static_cast<unsigned>(batch_here) * 256;
+    // B-fragment base of this lane: batch column g of n-tile 0 (every lane reads row 0 when XB == 1).
+    const unsigned x_lane = xs + static_cast<unsigned>(w_begin - c_begin) * (XB * 256) +
+                            ((XB == 1 ? 0 : g) * 4 + t) * 16;
 
     // Four registers that stay zero: the C operand of the first MMA of every chunk.
     float zero[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) asm volatile("mov.f32 %0, 0f00000000;" : "=f"(zero[j]));
 
-    float* red = red_all + group * kRedFloats;
-    int parity = 0;
-    unsigned c_waddr = ring + tid * 16;
-    unsigned c_saddr = ring + kScaleOffset + tid * 4;
-
     // Registers of one step: U chunks of packed words for 2*TILES rows, and their scale pairs.
     struct StepRegs {
         uint4 w[U][TILES][2];
         uint32_t s[TILES][2];
     };
-    int my_tiles = 0;
-    if (first_tile < p.row_tiles_total) my_tiles = (p.row_tiles_total - 1 - first_tile) / tile_stride + 1;
+    StepRegs buf[2];
+
     int steps_left = my_tiles * steps_per_tile;   // steps this warp still has to consume
-    int scale_row0 = first_tile * kRowsPerTile;   // only used by the U == 1 scale loads
+    int scale_row0 = first_tile * kRowsPerTile;   // walked only by the U == 1 scale loads
     int scale_step = 0;
 
-    auto load_step = [&](StepRegs& regs) {
-#pragma unroll
-        for (int tl = 0; tl < TILES; ++tl) {
+    auto load_step = [&](StepRegs& regs, auto slot_tag) {
+        constexpr int SLOT = decltype(slot_tag)::value;
+        auto item = [&](auto index_tag) -> uint4 {
+            return lds16<SLOT * kStageBytes + decltype(index_tag)::value * kItemBytes>(ring_w);
+        };
+        auto scale = [&](auto index_tag) -> uint32_t {
+            return lds4<SLOT * kStageBytes + decltype(index_tag)::value * 32>(ring_s + g * 4);
+        };
+        if constexpr (U == 2) {
+            // item (tile, half, chunk) = ((tile*2 + half) * 2 + chunk); scale pair of row tile*16 + half*8 + g
+            regs.w[0][0][0] = item(std::integral_constant<int, 0>{});
+            regs.w[1][0][0] = item(std::integral_constant<int, 1>{});
+            regs.w[0][0][1] = item(std::integral_constant<int, 2>{});
+            regs.w[1][0][1] = item(std::integral_constant<int, 3>{});
+            regs.s[0][0] = scale(std::integral_constant<int, 0>{});
+            regs.s[0][1] = scale(std::integral_constant<int, 1>{});
+            if constexpr (TILES == 2) {
+                regs.w[0][1][0] = item(std::integral_constant<int, 4>{});
+                regs.w[1][1][0] = item(std::integral_constant<int, 5>{});
+                regs.w[0][1][1] = item(std::integral_constant<int, 6>{});
+                regs.w[1][1][1] = item(std::integral_constant<int, 7>{});
+                regs.s[1][0] = scale(std::integral_constant<int, 2>{});
+                regs.s[1][1] = scale(std::integral_constant<int, 3>{});
+            }
+        } else {
+            regs.w[0][0][0] = item(std::integral_constant<int, 0>{});
+            regs.w[0][0][1] = item(std::integral_constant<int, 1>{});
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                for (int u = 0; u < U; ++u) regs.w[u][tl][h] = lds16(c_waddr + ((tl * 2 + h) * U + u) * kItemBytes);
-                if constexpr (U == 2) {
-                    regs.s[tl][h] = lds4(c_saddr + (tl * 2 + h) * (kThreads * 4));
-                } else {
-                    const int r = min(scale_row0 + tl * 16 + h * 8 + g, p.N - 1);
-                    regs.s[tl][h] = ldg_nc_u16(p.scales + static_cast<size_t>(r) * p.chunks + w_begin + scale_step);
-                }
+                const int r = min(scale_row0 + h * 8 + g, p.N - 1);
+                regs.s[0][h] = ldg_nc_u16(p.scales + static_cast<size_t>(r) * p.chunks + w_begin + scale_step);
             }
-        }
-        if constexpr (U == 1) {
             if (++scale_step == steps_per_tile) {
                 scale_step = 0;
                 scale_row0 += tile_stride * kRowsPerTile;
             }
         }
-        c_waddr += kStageBytes;
-        c_saddr += kStageBytes;
-        if (c_waddr >= ring_end) {
-            c_waddr -= ring_bytes;
-            c_saddr -= ring_bytes;
-        }
     };
 
-    StepRegs cur, nxt;
-    if (steps_left > 0) {
-        cp_async_wait(p.stages - 1);   // the oldest group has landed
-        load_step(cur);
-    }
+    float total[TILES][NT][4];
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) total[tl][nt][j] = 0.f;
 
-    for (int tile = first_tile; tile < p.row_tiles_total; tile += tile_stride) {
-        float total[TILES][NT][4];
-#pragma unroll
-        for (int tl = 0; tl < TILES; ++tl)
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) total[tl][nt][j] = 0.f;
-        const int row0 = tile * kRowsPerTile;
-        unsigned x_chunk[NT];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) x_chunk[nt] = x_lane[nt];
+    unsigned x_step = x_lane;   // B-fragment address of the current step's first chunk
 
-        for (int step = 0; step < steps_per_tile; ++step) {
-            // Pull the next step's words out of shared memory before computing on this one, so the
-            // shared-memory latency hides behind the unpack/MMA work of the current step.
-            if (steps_left > 1) {
-                cp_async_wait(p.stages - 2);
-                load_step(nxt);
+    // B fragment of (chunk u of the step, word i, n-tile nt): compile-time offsets from x_step.
+    auto load_b = [&](auto u_tag, auto i_tag, auto nt_tag) -> uint4 {
+        constexpr int OFFSET = decltype(u_tag)::value * (XB * 256) + decltype(i_tag)::value * (XB * 64) +
+                               decltype(nt_tag)::value * 512;
+        return lds16<OFFSET>(x_step);
+    };
+
+    auto compute_chunk = [&](const StepRegs& regs, auto u_tag) {
+        constexpr int u = decltype(u_tag)::value;
+        float acc[TILES][NT][4];
+        auto word_step = [&](auto i_tag) {
+            constexpr int i = decltype(i_tag)::value;
+            uint4 b[NT];
+            if constexpr (NT >= 1) b[0] = load_b(u_tag, i_tag, std::integral_constant<int, 0>{});
+            if constexpr (NT >= 2) b[1] = load_b(u_tag, i_tag, std::integral_constant<int, 1>{});
+            if constexpr (NT >= 4) {
+                b[2] = load_b(u_tag, i_tag, std::integral_constant<int, 2>{});
+                b[3] = load_b(u_tag, i_tag, std::integral_constant<int, 3>{});
             }
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                float acc[TILES][NT][4];
+            for (int tl = 0; tl < TILES; ++tl) {
+                const uint4 lo = regs.w[u][tl][0];
+                const uint4 hi = regs.w[u][tl][1];
+                const uint32_t word_lo = i == 0 ? lo.x : i == 1 ? lo.y : i == 2 ? lo.z : lo.w;
+                const uint32_t word_hi = i == 0 ? hi.x : i == 1 ? hi.y : i == 2 ? hi.z : hi.w;
+                uint32_t a_lo[4], a_hi[4];
+                unpack8(word_lo, a_lo);
+                unpack8(word_hi, a_hi);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint4 b[NT];
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) b[nt] = lds16(x_chunk[nt] + i * x_i_stride);
-#pragma unroll
-                    for (int tl = 0; tl < TILES; ++tl) {
-                        const uint4 lo = cur.w[u][tl][0];
-                        const uint4 hi = cur.w[u][tl][1];
-                        const uint32_t word_lo = i == 0 ? lo.x : i == 1 ? lo.y : i == 2 ? lo.z : lo.w;
-                        const uint32_t word_hi = i == 0 ? hi.x : i == 1 ? hi.y : i == 2 ? hi.z : hi.w;
-                        uint32_t a_lo[4], a_hi[4];
-                        unpack8(word_lo, a_lo);
-                        unpack8(word_hi, a_hi);
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            if (i == 0) {   // the chunk's first product starts from the zero registers
-                                mma_m16n8k16_from(acc[tl][nt], zero, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[nt].x, b[nt].y);
-                            } else {
-                                mma_m16n8k16(acc[tl][nt], a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[nt].x, b[nt].y);
-                            }
-                            mma_m16n8k16(acc[tl][nt], a_lo[2], a_hi[2], a_lo[3], a_hi[3], b[nt].z, b[nt].w);
-                        }
+                for (int nt = 0; nt < NT; ++nt) {
+                    if constexpr (i == 0) {   // the chunk's first product starts from the zero registers
+                        mma_m16n8k16_from(acc[tl][nt], zero, a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[nt].x, b[nt].y);
+                    } else {
+                        mma_m16n8k16(acc[tl][nt], a_lo[0], a_hi[0], a_lo[1], a_hi[1], b[nt].x, b[nt].y);
                     }
+                    mma_m16n8k16(acc[tl][nt], a_lo[2], a_hi[2], a_lo[3], a_hi[3], b[nt].z, b[nt].w);
                 }
-#pragma unroll
-                for (int tl = 0; tl < TILES; ++tl) {
-                    const __half2 pair_lo = *reinterpret_cast<const __half2*>(&cur.s[tl][0]);
-                    const __half2 pair_hi = *reinterpret_cast<const __half2*>(&cur.s[tl][1]);
-                    const float s_lo = u == 0 ? __low2float(pair_lo) : __high2float(pair_lo);
-                    const float s_hi = u == 0 ? __low2float(pair_hi) : __high2float(pair_hi);
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        total[tl][nt][0] = fmaf(acc[tl][nt][0], s_lo, total[tl][nt][0]);
-                        total[tl][nt][1] = fmaf(acc[tl][nt][1], s_lo, total[tl][nt][1]);
-                        total[tl][nt][2] = fmaf(acc[tl][nt][2], s_hi, total[tl][nt][2]);
-                        total[tl][nt][3] = fmaf(acc[tl][nt][3], s_hi, total[tl][nt][3]);
-                    }
-                }
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) x_chunk[nt] += x_chunk_stride;
             }
-            // The slot this step came from was emptied into registers one step ago: refill it.
-            issue_step();
-            --steps_left;
-            cur = nxt;
+        };
+        word_step(std::integral_constant<int, 0>{});
+        word_step(std::integral_constant<int, 1>{});
+        word_step(std::integral_constant<int, 2>{});
+        word_step(std::integral_constant<int, 3>{});
+#pragma unroll
+        for (int tl = 0; tl < TILES; ++tl) {
+            const __half2 pair_lo = *reinterpret_cast<const __half2*>(&regs.s[tl][0]);
+            const __half2 pair_hi = *reinterpret_cast<const __half2*>(&regs.s[tl][1]);
+            const float s_lo = u == 0 ? __low2float(pair_lo) : __high2float(pair_lo);
+            const float s_hi = u == 0 ? __low2float(pair_hi) : __high2float(pair_hi);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                total[tl][nt][0] = fmaf(acc[tl][nt][0], s_lo, total[tl][nt][0]);
+                total[tl][nt][1] = fmaf(acc[tl][nt][1], s_lo, total[tl][nt][1]);
+                total[tl][nt][2] = fmaf(acc[tl][nt][2], s_hi, total[tl][nt][2]);
+                total[tl][nt][3] = fmaf(acc[tl][nt][3], s_hi, total[tl][nt][3]);
+            }
         }
+    };
+    auto compute_step = [&](const StepRegs& regs) {
+        compute_chunk(regs, std::integral_constant<int, 0>{});
+        if constexpr (U == 2) compute_chunk(regs, std::integral_constant<int, 1>{});
+        x_step += U * XB * 256;
+    };
 
-        // ---- combine the KW warps of the group ------------------------------------------------
+    float* red = red_all + group * kRedFloats;
+    int parity = 0;
+    const int gthread = kw * 32 + lane;   // thread index inside the group
+    const bool split_k = p.k_splits > 1;
+
+    // Combines the group's warps for one finished row tile and writes it out (or hands it to the
+    // split-K reduction); leaves `total` cleared for the next tile.
+    auto finish_tile = [&](int tile) {
+        const int row0 = tile * kRowsPerTile;
         const int outputs = kRowsPerTile * batch_here;
-        const bool split_k = p.k_splits > 1;
-        float* buf = red + parity * (KW * kAccPerLane * 32);
+        float* stage = red + parity * (KW * kAccPerLane * 32);
+        auto store = [&](int row, size_t m, float sum) {
+            if (split_k) {
+                p.partial[(static_cast<size_t>(split) * p.M + m) * p.N + row] = sum;
+            } else if (p.out_f32) {
+                static_cast<float*>(p.y)[m * p.N + row] = sum;
+            } else {
+                static_cast<__half*>(p.y)[m * p.N + row] = __float2half_rn(sum);
+            }
+        };
         if constexpr (KW > 1) {
 #pragma unroll
             for (int tl = 0; tl < TILES; ++tl)
@@ -400,11 +454,8 @@ linear_mma_kernel(const MmaParams p) {
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        buf[(kw * kAccPerLane + (tl * NT + nt) * 4 + j) * 32 + lane] = total[tl][nt][j];
+                        stage[(kw * kAccPerLane + (tl * NT + nt) * 4 + j) * 32 + lane] = total[tl][nt][j];
             group_barrier(1 + group, KW * 32);
-        }
-        const int gthread = kw * 32 + lane;   // thread index inside the group
-        if constexpr (KW > 1) {
             for (int e = gthread; e < outputs; e += KW * 32) {
                 const int rl = e % kRowsPerTile;   // consecutive threads -> consecutive rows of y
                 const int col = e / kRowsPerTile;
@@ -414,18 +465,8 @@ linear_mma_kernel(const MmaParams p) {
                 const int src_lane = (rr & 7) * 4 + (cc >> 1);
                 float sum = 0.f;
 #pragma unroll
-                for (int w = 0; w < KW; ++w) sum += buf[(w * kAccPerLane + (tl * NT + nt) * 4 + j) * 32 + src_lane];
-                const int row = row0 + rl;
-                const size_t m = m0 + col;
-                if (row < p.N) {
-                    if (split_k) {
-                        p.partial[(static_cast<size_t>(split) * p.M + m) * p.N + row] = sum;
-                    } else if (p.out_f32) {
-                        static_cast<float*>(p.y)[m * p.N + row] = sum;
-                    } else {
-                        static_cast<__half*>(p.y)[m * p.N + row] = __float2half_rn(sum);
-                    }
-                }
+                for (int w = 0; w < KW; ++w) sum += stage[(w * kAccPerLane + (tl * NT + nt) * 4 + j) * 32 + src_lane];
+                if (row0 + rl < p.N) store(row0 + rl, m0 + col, sum);
             }
         } else {
             // one warp owns the tile: write straight from the accumulator registers
@@ -437,23 +478,19 @@ linear_mma_kernel(const MmaParams p) {
                     for (int j = 0; j < 4; ++j) {
                         const int row = row0 + tl * 16 + (j >> 1) * 8 + g;
                         const int col = nt * 8 + 2 * t + (j & 1);
-                        const size_t m = m0 + col;
-                        if (row < p.N && col < batch_here) {
-                            const float sum = total[tl][nt][j];
-                            if (split_k) {
-                                p.partial[(static_cast<size_t>(split) * p.M + m) * p.N + row] = sum;
-                            } else if (p.out_f32) {
-                                static_cast<float*>(p.y)[m * p.N + row] = sum;
-                            } else {
-                                static_cast<__half*>(p.y)[m * p.N + row] = __float2half_rn(sum);
-                            }
-                        }
+                        if (row < p.N && col < batch_here) store(row, m0 + col, total[tl][nt][j]);
                     }
         }
         parity ^= 1;
+#pragma unroll
+        for (int tl = 0; tl < TILES; ++tl)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) total[tl][nt][j] = 0.f;
 
         if (split_k) {
-            // ---- combine K-split CTAs: the group arriving last sums the partials in split order
+            // The group arriving last at this tile sums the partials of all K splits in split order.
             __threadfence();
             group_barrier(1 + group, KW * 32);
             unsigned* counter = p.counters + (static_cast<size_t>(blockIdx.z) * p.row_tiles_total + tile);
@@ -462,14 +499,11 @@ linear_mma_kernel(const MmaParams p) {
                 last_flag[group] = arrived == static_cast<unsigned>(p.k_splits - 1);
             }
             group_barrier(1 + group, KW * 32);
-            const bool is_last = last_flag[group] != 0;
-            if (is_last) {
+            if (last_flag[group] != 0) {
                 __threadfence();
                 for (int e = gthread; e < outputs; e += KW * 32) {
-                    const int rl = e % kRowsPerTile;
-                    const int col = e / kRowsPerTile;
-                    const int row = row0 + rl;
-                    const size_t m = m0 + col;
+                    const int row = row0 + e % kRowsPerTile;
+                    const size_t m = m0 + e / kRowsPerTile;
                     if (row >= p.N) continue;
                     float sum = 0.f;
                     for (int s = 0; s < p.k_splits; ++s) {
@@ -483,10 +517,94 @@ linear_mma_kernel(const MmaParams p) {
                 }
                 if (gthread == 0) *counter = 0u;   // ready for the next call sharing the workspace
             }
-            group_barrier(1 + group, KW * 32);   // last_flag may be rewritten by the next tile
+            group_barrier(1 + group, KW * 32);   // last_flag may be rewritten at the next tile
+        }
+    };
+
+    if (steps_per_tile == 0) {
+        // A warp without a share of K still meets its group at every tile's barrier.
+        for (int tile = first_tile; tile < p.row_tiles_total; tile += tile_stride) finish_tile(tile);
+        cp_async_wait<0>();
+        return;
+    }
+
+    if (steps_left > 0) {
+        cp_async_wait<STAGES - 1>();   // the oldest group, slot 0, has landed
+        __syncwarp();                  // ... for every lane of the warp
+        load_step(buf[0], std::integral_constant<int, 0>{});
+    }
+    int tile = first_tile;
+    int tile_steps_left = steps_per_tile;
+
+    // One position of the unrolled step loop: POS fixes the ring slot and the register buffer.
+    // Returns true when the step completed the current row tile.
+    auto step_at = [&](auto pos_tag) -> bool {
+        constexpr int POS = decltype(pos_tag)::value;
+        constexpr int NEXT_SLOT = (POS + 1) % STAGES;
+        constexpr int PRODUCER_POS = (POS + STAGES) % kPeriod;   // the producer runs STAGES steps ahead
+        // The warp-wide sync publishes the lanes' landed copies to each other; it also orders the
+        // refill below after every lane's reads of that slot (done one step ago).
+        cp_async_wait<STAGES - 2>();
+        __syncwarp();
+        // Pull the next step's words out of shared memory before computing on this one, so the
+        // shared-memory latency hides behind the current step's unpack and MMA work.
+        // (Past the last step this reads a stale slot into registers nobody uses.)
+        load_step(buf[(POS + 1) & 1], std::integral_constant<int, NEXT_SLOT>{});
+        compute_step(buf[POS & 1]);
+        // This step's slot was emptied into registers one step ago: refill it.
+        issue_step(std::integral_constant<int, PRODUCER_POS>{});
+        --steps_left;
+        return --tile_steps_left == 0;
+    };
+
+    // The step code exists once per ring position and the tile epilogue once: a step that finishes
+    // a tile leaves the switch, the epilogue runs, and the switch is re-entered at the next position.
+    int pos = 0;
+    while (steps_left > 0) {
+        bool tile_done = false;
+        switch (pos) {
+            case 0:
+                tile_done = step_at(std::integral_constant<int, 0>{});
+                pos = 1;
+                if (tile_done || steps_left == 0) break;
+                [[fallthrough]];
+            case 1:
+                tile_done = step_at(std::integral_constant<int, 1>{});
+                pos = 2;
+                if (tile_done || steps_left == 0) break;
+                [[fallthrough]];
+            case 2:
+                tile_done = step_at(std::integral_constant<int, 2>{});
+                pos = 3;
+                if (tile_done || steps_left == 0) break;
+                [[fallthrough]];
+            case 3:
+                tile_done = step_at(std::integral_constant<int, 3>{});
+                pos = kPeriod == 4 ? 0 : 4;
+                if (kPeriod == 4 || tile_done || steps_left == 0) break;
+                [[fallthrough]];
+            case 4:
+                if constexpr (kPeriod == 6) {
+                    tile_done = step_at(std::integral_constant<int, 4>{});
+                    pos = 5;
+                    if (tile_done || steps_left == 0) break;
+                }
+                [[fallthrough]];
+            default:
+                if constexpr (kPeriod == 6) {
+                    tile_done = step_at(std::integral_constant<int, 5>{});
+                    pos = 0;
+                }
+                break;
+        }
+        if (tile_done) {
+            finish_tile(tile);
+            tile += tile_stride;
+            tile_steps_left = steps_per_tile;
+            x_step = x_lane;
         }
     }
-    cp_async_wait(0);   // nothing of this thread may still be landing in shared memory at exit
+    cp_async_wait<0>();   // nothing of this thread may still be landing in shared memory at exit
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -494,54 +612,71 @@ struct Variant {
     const void* fn;
     int red_bytes;     // shared memory for the cross-warp reduction
     int stage_bytes;   // shared memory of one pipeline stage
+    int stages;
+    int x_rows;        // batch rows stored per chunk of x (XB)
 };
 
-template <int NT, int TILES, int KW, int U>
+template <int NT, int XB, int TILES, int KW, int U, int STAGES>
 Variant variant_of() {
     constexpr int RW = kWarpsPerCta / KW;
     constexpr int red = KW > 1 ? 2 * KW * TILES * NT * 4 * 32 * RW * static_cast<int>(sizeof(float)) : 0;
-    return {reinterpret_cast<const void*>(&linear_mma_kernel<NT, TILES, KW, U>), red, stage_bytes<TILES, U>()};
+    return {reinterpret_cast<const void*>(&linear_mma_kernel<NT, XB, TILES, KW, U, STAGES>), red,
+            stage_bytes<TILES, U>(), STAGES, XB};
 }
 
-template <int NT, int TILES, int KW>
-bool pick_unroll(int unroll, Variant* v) {
-    switch (unroll) {
-        case 1: *v = variant_of<NT, TILES, KW, 1>(); return true;
-        case 2: *v = variant_of<NT, TILES, KW, 2>(); return true;
-        default: return false;
+template <int NT, int XB, int TILES, int KW>
+bool pick_pipeline(int unroll, int stages, Variant* v) {
+    if (unroll == 1) {   // odd K/128: the slow-scale path, one tile per warp and one ring depth only
+        if constexpr (TILES == 1) {
+            if (stages != 3) return false;
+            *v = variant_of<NT, XB, 1, KW, 1, 3>();
+            return true;
+        } else {
+            return false;
+        }
     }
+    if (unroll != 2) return false;
+    if (stages == 3) { *v = variant_of<NT, XB, TILES, KW, 2, 3>(); return true; }
+    if (stages == 4) { *v = variant_of<NT, XB, TILES, KW, 2, 4>(); return true; }
+    return false;
 }
 
-template <int NT, int TILES>
-bool pick_kw(int kw, int unroll, Variant* v) {
+template <int NT, int XB, int TILES>
+bool pick_kw(int kw, int unroll, int stages, Variant* v) {
     switch (kw) {
-        case 1: return pick_unroll<NT, TILES, 1>(unroll, v);
-        case 2: return pick_unroll<NT, TILES, 2>(unroll, v);
-        case 4: return pick_unroll<NT, TILES, 4>(unroll, v);
-        case 8: return pick_unroll<NT, TILES, 8>(unroll, v);
+        case 1: return pick_pipeline<NT, XB, TILES, 1>(unroll, stages, v);
+        case 2: return pick_pipeline<NT, XB, TILES, 2>(unroll, stages, v);
+        case 4: return pick_pipeline<NT, XB, TILES, 4>(unroll, stages, v);
+        case 8: return pick_pipeline<NT, XB, TILES, 8>(unroll, stages, v);
         default: return false;
     }
 }
 
-template <int NT>
+template <int NT, int XB>
 bool pick_tiles(const w4a16_linear_config& c, Variant* v) {
     switch (c.row_tiles) {
-        case 1: return pick_kw<NT, 1>(c.k_warps, c.unroll, v);
-        case 2: return NT <= 2 ? pick_kw<(NT <= 2 ? NT : 1), 2>(c.k_warps, c.unroll, v) : false;
+        case 1: return pick_kw<NT, XB, 1>(c.k_warps, c.unroll, c.stages, v);
+        case 2:
+            if constexpr (NT <= 2) {
+                return pick_kw<NT, XB, 2>(c.k_warps, c.unroll, c.stages, v);
+            } else {
+                return false;
+            }
         default: return false;
     }
 }
 
-bool pick_variant(int nt, const w4a16_linear_config& c, Variant* v) {
+bool pick_variant(int nt, bool single_row, const w4a16_linear_config& c, Variant* v) {
     switch (nt) {
-        case 1: return pick_tiles<1>(c, v);
-        case 2: return pick_tiles<2>(c, v);
-        case 4: return pick_tiles<4>(c, v);
+        case 1: return single_row ? pick_tiles<1, 1>(c, v) : pick_tiles<1, 8>(c, v);
+        case 2: return pick_tiles<2, 16>(c, v);
+        case 4: return pick_tiles<4, 32>(c, v);
         default: return false;
     }
 }
 
 int batch_tiles_for(int64_t M) { return M <= 8 ? 1 : (M <= 16 ? 2 : 4); }
+int x_rows_for(int64_t M) { return M == 1 ? 1 : 8 * batch_tiles_for(M); }
 
 int sm_count() {
     static int cached = 0;
@@ -557,8 +692,8 @@ int sm_count() {
     return cached;
 }
 
-// Bytes of x a CTA must hold for `batch` rows of a K slice of `chunks` chunks.
-size_t x_slice_bytes(int batch, int chunks) { return static_cast<size_t>(batch) * chunks * kGroup * sizeof(__half); }
+// Bytes of x a CTA holds for `rows` stored batch rows of a K slice of `chunks` chunks.
+size_t x_slice_bytes(int rows, int chunks) { return static_cast<size_t>(rows) * chunks * kGroup * sizeof(__half); }
 
 }  // namespace
 
@@ -578,41 +713,56 @@ w4a16_linear_config choose_linear_config(int64_t M, int64_t N, int64_t K, int ma
     const int sms = 148;
     w4a16_linear_config c;
     const int nt = batch_tiles_for(M);
-    const int batch = static_cast<int>(M < 8 * nt ? M : 8 * nt);
+    const int x_rows = x_rows_for(M);
     const int64_t batch_blocks = (M + 8 * nt - 1) / (8 * nt);
     const int chunks = static_cast<int>(K / kGroup);
     const int64_t tiles16 = (N + 15) / 16;
 
     c.row_tiles = 1;
-    // Warps needed to keep every SM streaming: about 16 per SM.  Split K inside the CTA first
-    // (free), across CTAs second (costs a round trip through the workspace).
-    const int64_t want_warps = static_cast<int64_t>(sms) * 16;
+    c.unroll = chunks % 2 == 0 ? 2 : 1;
+    // Warps of a CTA that share one row tile.  Two pulls, both measured on B200 (sweeps over the
+    // TinyLlama and Llama-70B shapes): enough warps to keep every SM streaming (about 12 per SM)
+    // when there are few row tiles, and no more than about 16 chunks of K per warp and tile, which
+    // keeps the tail of the persistent loop short.
+    const int64_t want_warps = static_cast<int64_t>(sms) * 12;
     int kw = 1;
-    while (kw < 8 && tiles16 * batch_blocks * kw < want_warps && chunks >= kw * 2) kw *= 2;
+    while (kw < 8 && tiles16 * batch_blocks * kw < want_warps && chunks >= kw * 2 * c.unroll) kw *= 2;
+    while (kw < 8 && chunks / kw > 16 && chunks >= kw * 2 * c.unroll) kw *= 2;
     c.k_warps = kw;
+    // Splitting K across CTAs costs a round trip through the workspace; do it when the row tiles
+    // alone cannot fill the machine ...
     int splits = 1;
     if (M <= 32) {
         while (splits * 2 <= max_splits && splits * 2 <= kMaxKSplits &&
-               tiles16 * batch_blocks * kw * splits < want_warps && chunks >= splits * 2 * kw * 2) {
+               tiles16 * batch_blocks * kw * splits < want_warps && chunks >= splits * 2 * kw * 2 * c.unroll) {
             splits *= 2;
         }
     }
-    // The activation slice of a CTA has to fit in shared memory.
-    while (x_slice_bytes(batch, (chunks + splits - 1) / splits) > static_cast<size_t>(kSmemBudget - 80 * 1024) &&
+    // ... or, for the single-row case, when the activation slice would crowd the copy ring out of
+    // shared memory (two CTAs per SM want it at or below 32 KB) ...
+    if (M == 1) {
+        while (x_slice_bytes(x_rows, (chunks + splits - 1) / splits) > 32u * 1024 && splits * 2 <= max_splits &&
+               splits * 2 <= kMaxKSplits && chunks >= splits * 2 * kw * c.unroll) {
+            splits *= 2;
+        }
+    }
+    // ... and always when the slice would not fit next to a three-slot ring at all.
+    while (x_slice_bytes(x_rows, (chunks + splits - 1) / splits) > static_cast<size_t>(kSmemBudget - 64 * 1024) &&
            splits * 2 <= max_splits && splits * 2 <= kMaxKSplits && chunks >= splits * 2) {
         splits *= 2;
     }
     c.k_splits = splits;
-    c.unroll = chunks % 2 == 0 ? 2 : 1;
-    c.stages = 0;   // sized at launch from the shared memory left over
+    c.stages = 0;   // chosen at launch from the shared memory left over
     return c;
 }
 
-int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg, bool programmatic,
+int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_in, bool programmatic,
                       bool out_f32, cudaStream_t stream) {
     if (prob.group != kGroup || prob.K % kGroup != 0) return W4A16_ERR_BAD_CONFIG;
     if (prob.M > INT32_MAX || prob.N > INT32_MAX || prob.K > INT32_MAX) return W4A16_ERR_TOO_LARGE;
+    w4a16_linear_config cfg = cfg_in;
     const int nt = batch_tiles_for(prob.M);
+    const int x_rows = x_rows_for(prob.M);
     const int chunks = static_cast<int>(prob.K / kGroup);
     const int splits = cfg.k_splits;
     if (splits < 1 || splits > kMaxKSplits || splits > chunks) return W4A16_ERR_BAD_CONFIG;
@@ -621,10 +771,25 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg,
     if (cfg.unroll == 2 && (chunks % 2 != 0 || reinterpret_cast<uintptr_t>(prob.scales) % 4 != 0)) {
         return W4A16_ERR_BAD_CONFIG;
     }
-    if (cfg.stages < 0 || (cfg.stages > 0 && cfg.stages < 3) || cfg.stages > kMaxStages) return W4A16_ERR_BAD_CONFIG;
+    if (cfg.unroll != 1 && cfg.unroll != 2) return W4A16_ERR_BAD_CONFIG;
+    if (cfg.stages != 0 && cfg.stages != 3 && cfg.stages != 4) return W4A16_ERR_BAD_CONFIG;
 
+    const int per_split = (chunks + splits - 1) / splits;
+    const int chunks_per_split = (per_split + cfg.unroll - 1) / cfg.unroll * cfg.unroll;
+    if ((splits - 1) * chunks_per_split >= chunks) return W4A16_ERR_BAD_CONFIG;   // an empty split
+
+    // Ring depth: four slots when two CTAs still fit on an SM with them, else three.
     Variant variant;
-    if (!pick_variant(nt, cfg, &variant)) return W4A16_ERR_BAD_CONFIG;
+    if (cfg.stages == 0) {
+        cfg.stages = cfg.unroll == 1 ? 3 : 4;
+        if (cfg.unroll == 2) {
+            if (!pick_variant(nt, prob.M == 1, cfg, &variant)) return W4A16_ERR_BAD_CONFIG;
+            const size_t with_four =
+                kFlagBytes + variant.red_bytes + x_slice_bytes(x_rows, chunks_per_split) + 4u * variant.stage_bytes;
+            if (with_four > static_cast<size_t>(kSmemPerSm / 2 - 1024)) cfg.stages = 3;
+        }
+    }
+    if (!pick_variant(nt, prob.M == 1, cfg, &variant)) return W4A16_ERR_BAD_CONFIG;
 
     MmaParams params;
     params.x = prob.x;
@@ -637,12 +802,10 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg,
     params.N = static_cast<int>(prob.N);
     params.K = static_cast<int>(prob.K);
     params.chunks = chunks;
-    const int per_split = (chunks + splits - 1) / splits;
-    params.chunks_per_split = (per_split + cfg.unroll - 1) / cfg.unroll * cfg.unroll;
+    params.chunks_per_split = chunks_per_split;
     params.k_splits = splits;
     params.row_tiles_total = static_cast<int>((prob.N + 16 * cfg.row_tiles - 1) / (16 * cfg.row_tiles));
     params.out_f32 = out_f32 ? 1 : 0;
-    if ((splits - 1) * params.chunks_per_split >= chunks) return W4A16_ERR_BAD_CONFIG;   // an empty split
     if (splits > 1) {
         const size_t need = linear_workspace_bytes_for(prob.M, prob.N, splits);
         if (prob.workspace == nullptr || prob.workspace_bytes < need) return W4A16_ERR_WORKSPACE;
@@ -652,22 +815,9 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg,
                                                   linear_counter_bytes(prob.M, prob.N));
     }
 
-    const int batch = static_cast<int>(prob.M < 8 * nt ? prob.M : 8 * nt);
-    const size_t fixed = static_cast<size_t>(variant.red_bytes) + x_slice_bytes(batch, params.chunks_per_split);
-    int stages = cfg.stages;
-    if (stages == 0) {
-        // Deepest ring that still lets three, else two, else one CTA share an SM; at least three
-        // slots in flight per thread before giving up residency.
-        for (int ctas = 3; ctas >= 1 && stages == 0; --ctas) {
-            const int64_t room = static_cast<int64_t>(kSmemPerSm / ctas - 1024) - static_cast<int64_t>(fixed);
-            const int64_t fit = room / variant.stage_bytes;
-            if (fit >= (ctas > 1 ? 4 : 3)) stages = static_cast<int>(fit < kMaxStages ? fit : kMaxStages);
-        }
-        if (stages == 0) return W4A16_ERR_WORKSPACE;   // activation slice too large: needs more K splits
-    }
-    const size_t smem = fixed + static_cast<size_t>(stages) * variant.stage_bytes;
-    if (smem > static_cast<size_t>(kSmemBudget)) return W4A16_ERR_WORKSPACE;
-    params.stages = stages;
+    const size_t smem = kFlagBytes + static_cast<size_t>(variant.red_bytes) + x_slice_bytes(x_rows, chunks_per_split) +
+                        static_cast<size_t>(variant.stages) * variant.stage_bytes;
+    if (smem > static_cast<size_t>(kSmemBudget)) return W4A16_ERR_WORKSPACE;   // x slice too large: more K splits
 
     // Opt in to large dynamic shared memory once per kernel variant, and learn its occupancy
     // (cached per variant and shared-memory size; one process drives one device).
