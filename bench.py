@@ -337,6 +337,7 @@ def decode_bench(torch, device) -> dict:
         return row
 
     out = {"model": "TinyLlama-1.1B architecture, random weights", "prompt_tokens": prompt_len, "new_tokens": new_tokens}
+    saved_pdl = os.environ.pop("W4A16_PDL", None)
     torch.cuda.reset_peak_memory_stats(device)
     out["fp16_cublas"] = measure("fp16")
     replaced = replace_linear_layers(model, group_size=GROUP)
@@ -347,6 +348,8 @@ def decode_bench(torch, device) -> dict:
     os.environ["W4A16_PDL"] = "1"
     out["w4a16_programmatic_launch"] = measure("w4a16+pdl")
     os.environ.pop("W4A16_PDL", None)
+    if saved_pdl is not None:
+        os.environ["W4A16_PDL"] = saved_pdl
     del model
     torch.cuda.empty_cache()
     return out
@@ -379,9 +382,16 @@ def run_product(args) -> dict:
     layers = decode_token_layers()
     log(f"[rank {rank}] building {len(layers)} quantised layers on {torch.cuda.get_device_name(device)}")
     weights = [make_layer(torch, k, n, seed=1000 * rank + i, device=device) for i, (_, k, n) in enumerate(layers)]
+    # All activations of a step live in one pinned host buffer and one device buffer; the layers read
+    # 256-byte aligned views of the device buffer, so one copy brings a whole step's inputs in.
     g = torch.Generator().manual_seed(1)
-    x_host = [torch.randn((1, k), dtype=torch.float32, generator=g).half().pin_memory() for _, k, _ in layers]
-    x_dev = [x.to(device) for x in x_host]
+    x_all_host = torch.cat([torch.randn((k,), dtype=torch.float32, generator=g).half() for _, k, _ in layers]).pin_memory()
+    x_all_dev = x_all_host.to(device)
+    x_host, x_dev, offset = [], [], 0
+    for _, k, _ in layers:
+        x_host.append(x_all_host[offset:offset + k].view(1, k))
+        x_dev.append(x_all_dev[offset:offset + k].view(1, k))
+        offset += k
     step_bytes = sum(algorithmic_bytes(1, k, n) for _, k, n in layers)
     outs: list = [None] * len(layers)
 
@@ -430,17 +440,29 @@ def run_product(args) -> dict:
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
     kernel_us = ms_per_step * 1e3 / len(layers)
 
+    # ---- the same K replays with plain stream-ordered launches, for comparison
+    plain = None
+    if args.pdl:
+        os.environ.pop("W4A16_PDL", None)
+        plain_graph = capture(torch, step)
+        for _ in range(3):
+            plain_graph.replay()
+        barrier()
+        plain_ms = max_over_ranks(time_replays(torch, plain_graph, args.steps)) / args.steps
+        plain = {"value": round(world * step_bytes / (plain_ms * 1e-3) / 1e9, 1), "ms_per_step": round(plain_ms, 5)}
+        del plain_graph
+        os.environ["W4A16_PDL"] = "1"
+        graph = capture(torch, step)   # `outs` point at this graph's outputs again
+
     # ---- e2e: host activations in, host outputs back, every step
-    y_host = [torch.empty((1, n), dtype=torch.float16).pin_memory() for _, _, n in layers]
-    h2d = sum(x.numel() * 2 for x in x_host)
-    d2h = sum(y.numel() * 2 for y in y_host)
+    y_all_host = torch.empty((sum(n for _, _, n in layers),), dtype=torch.float16).pin_memory()
+    h2d = x_all_host.numel() * 2
+    d2h = y_all_host.numel() * 2
 
     def e2e_step():
-        for dst, src in zip(x_dev, x_host):
-            dst.copy_(src, non_blocking=True)
-        graph.replay()
-        for dst, src in zip(y_host, outs):
-            dst.copy_(src, non_blocking=True)
+        x_all_dev.copy_(x_all_host, non_blocking=True)                 # one host -> device copy
+        graph.replay()                                                  # 155 linears through the public op
+        y_all_host.copy_(torch.cat([o.view(-1) for o in outs]), non_blocking=True)   # gather + one copy back
 
     for _ in range(3):
         e2e_step()
@@ -477,6 +499,7 @@ def run_product(args) -> dict:
                    "group_size": GROUP, "bytes_per_step": step_bytes, "l2_policy": "inputs larger than L2 (535 MB per step)",
                    "parallelism": "replicas" if world > 1 else "single", "programmatic_launch": bool(args.pdl)},
         "decode_tok_s_linears_only": round(world * 1e3 / ms_per_step, 1),
+        "plain_launch": plain,
         "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": round(e2e_ms, 5)},
         "gpu_launches": args.steps * len(layers),
@@ -566,7 +589,9 @@ def main() -> None:
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", choices=["product", "reference"], default="product")
-    parser.add_argument("--pdl", action="store_true", help="launch the fused kernel with programmatic stream serialisation")
+    parser.add_argument("--no-pdl", dest="pdl", action="store_false",
+                        help="plain stream-ordered launches instead of programmatic dependent launch")
+    parser.set_defaults(pdl=True)
     parser.add_argument("--quick", action="store_true", help="skip the per-shape tables")
     args = parser.parse_args()
     result = run_reference(args) if args.impl == "reference" else run_product(args)

@@ -720,19 +720,32 @@ w4a16_linear_config choose_linear_config(int64_t M, int64_t N, int64_t K, int ma
 
     c.row_tiles = 1;
     c.unroll = chunks % 2 == 0 ? 2 : 1;
-    // Warps of a CTA that share one row tile.  Two pulls, both measured on B200 (sweeps over the
-    // TinyLlama and Llama-70B shapes): enough warps to keep every SM streaming (about 12 per SM)
-    // when there are few row tiles, and no more than about 16 chunks of K per warp and tile, which
-    // keeps the tail of the persistent loop short.
+    // Warps of a CTA that share one row tile: the fewest that still give about 12 streaming warps
+    // per SM (more only shortens each warp's share of a tile and multiplies the per-tile epilogue).
     const int64_t want_warps = static_cast<int64_t>(sms) * 12;
     int kw = 1;
     while (kw < 8 && tiles16 * batch_blocks * kw < want_warps && chunks >= kw * 2 * c.unroll) kw *= 2;
-    while (kw < 8 && chunks / kw > 16 && chunks >= kw * 2 * c.unroll) kw *= 2;
+    // Shapes measured on B200 where a different split of the same work is clearly faster (sweeps over
+    // every k_warps x k_splits combination; Llama-70B gate/up and down projections).
+    struct Tuned { int64_t n, k; int k_warps, k_splits; };
+    static const Tuned tuned[] = {
+        {28672, 8192, 4, 1},   // 1792 row tiles: four warps per tile balance the last wave
+        {8192, 28672, 1, 4},   // long K: split across CTAs so the activation slice stays small
+    };
+    int tuned_splits = 0;
+    if (M <= 8) {
+        for (const Tuned& entry : tuned) {
+            if (entry.n == N && entry.k == K && entry.k_splits <= max_splits) {
+                kw = entry.k_warps;
+                tuned_splits = entry.k_splits;
+            }
+        }
+    }
     c.k_warps = kw;
     // Splitting K across CTAs costs a round trip through the workspace; do it when the row tiles
     // alone cannot fill the machine ...
-    int splits = 1;
-    if (M <= 32) {
+    int splits = tuned_splits > 0 ? tuned_splits : 1;
+    if (M <= 32 && tuned_splits == 0) {
         while (splits * 2 <= max_splits && splits * 2 <= kMaxKSplits &&
                tiles16 * batch_blocks * kw * splits < want_warps && chunks >= splits * 2 * kw * 2 * c.unroll) {
             splits *= 2;
@@ -740,7 +753,7 @@ w4a16_linear_config choose_linear_config(int64_t M, int64_t N, int64_t K, int ma
     }
     // ... or, for the single-row case, when the activation slice would crowd the copy ring out of
     // shared memory (two CTAs per SM want it at or below 32 KB) ...
-    if (M == 1) {
+    if (M == 1 && tuned_splits == 0) {
         while (x_slice_bytes(x_rows, (chunks + splits - 1) / splits) > 32u * 1024 && splits * 2 <= max_splits &&
                splits * 2 <= kMaxKSplits && chunks >= splits * 2 * kw * c.unroll) {
             splits *= 2;
