@@ -102,6 +102,26 @@ size_t w4a16_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int w4a16_dequantize_f16(const void* packed, const void* scales, void* weights,
                          int64_t N, int64_t K, int64_t group_size, w4a16_stream_t stream);
 
+/*
+ * w4a16_linear_f16 for callers that cannot allocate device memory (no cudaMalloc after start-up,
+ * no workspace handed to a plugin, an open stream capture): the split-K scratch is a fixed array
+ * inside the library's device image, w4a16_static_scratch_bytes() bytes per GPU, instead of a
+ * caller workspace.  This entry point has no counterpart in the reference project, which never
+ * splits K and so never needs scratch.
+ *
+ * Same arguments and results as w4a16_linear_f16 without the workspace pair.  It allocates and frees
+ * nothing.  Problems whose split-K scratch exceeds the array return W4A16_ERR_TOO_LARGE and launch
+ * nothing.  All calls on a device share the one array: calls that may overlap on the GPU (several
+ * streams, parallel graph branches) race; calls ordered on one stream do not.  The first call on
+ * each device resolves the array's address and should be made outside stream capture.
+ */
+int w4a16_linear_f16_static_scratch(const void* x, const void* packed, const void* scales, void* y,
+                                    int64_t M, int64_t N, int64_t K, int64_t group_size,
+                                    uint32_t flags, w4a16_stream_t stream);
+
+/* Size in bytes of the built-in scratch array used by w4a16_linear_f16_static_scratch. */
+size_t w4a16_static_scratch_bytes(void);
+
 /* Number of kernels this library has launched in this process (all entry points, all devices). */
 uint64_t w4a16_launch_count(void);
 

@@ -39,6 +39,8 @@ C_API = {
         [_P, _P, _P, _P, _I, _I, _I, _I, _P, ctypes.c_size_t, ctypes.c_uint32, ctypes.POINTER(LinearConfig), _P],
     ),
     "w4a16_linear_workspace_bytes": (ctypes.c_size_t, [_I, _I, _I]),
+    "w4a16_linear_f16_static_scratch": (ctypes.c_int, [_P, _P, _P, _P, _I, _I, _I, _I, ctypes.c_uint32, _P]),
+    "w4a16_static_scratch_bytes": (ctypes.c_size_t, []),
     "w4a16_dequantize_f16": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
     "w4a16_launch_count": (ctypes.c_uint64, []),
     "w4a16_status_string": (ctypes.c_char_p, [ctypes.c_int]),
