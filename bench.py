@@ -56,6 +56,9 @@ LLAMA70B = {
     "gate_up_proj": (8192, 28672),
     "down_proj": (28672, 8192),
 }
+# Mean DRAM bytes (read + write) per launch of the fused kernel over this workload, from one ncu
+# capture of the timed region (profiles/bench_timed_region_launch_list.md); algorithmic: 3,451,728.
+NCU_DRAM_BYTES_PER_LAUNCH = 3513170
 BLOCK_ORDER = ["qo_proj", "kv_proj", "kv_proj", "qo_proj", "gate_up_proj", "gate_up_proj", "down_proj"]
 N_BLOCKS = 22
 
@@ -355,6 +358,41 @@ def decode_bench(torch, device) -> dict:
     return out
 
 
+def run_single_layer(args) -> dict:
+    """A few launches of one layer shape over three weight copies: the small case profilers capture.
+
+    `--single-layer K N M`; every call goes through ``torch.ops.w4a16.linear``.
+    """
+    import torch
+
+    from nibble_b200 import linear_cuda
+
+    k, n, m = args.single_layer
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    packed, scales = make_layer(torch, k, n, seed=0, device=device)
+    copies = 3
+    pk = packed.unsqueeze(0).repeat(copies, 1, 1)
+    sc = scales.unsqueeze(0).repeat(copies, 1, 1)
+    x = torch.randn((m, k), device=device).half()
+    for i in range(4):
+        linear_cuda(x, pk[i % copies], sc[i % copies], GROUP)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()
+    start.record()
+    for i in range(args.steps):
+        linear_cuda(x, pk[i % copies], sc[i % copies], GROUP)
+    end.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    us = start.elapsed_time(end) * 1e3 / args.steps
+    payload = algorithmic_bytes(m, k, n)
+    peak, kind = measured_peaks()
+    return {"single_layer": {"K": k, "N": n, "M": m}, "launches": args.steps, "us_per_launch_eager": round(us, 2),
+            "gbs": round(payload / us / 1e3, 1), "peak": peak, "peak_kind": kind, "bytes_per_launch": payload}
+
+
 def run_product(args) -> dict:
     import torch
     import torch.distributed as dist
@@ -433,12 +471,24 @@ def run_product(args) -> dict:
     barrier()
     sampler.active.set()
     launches_before = lib.w4a16_launch_count()
+    torch.cuda.profiler.start()   # `ncu --profile-from-start off` captures exactly the timed region
     ms = time_replays(torch, graph, args.steps)
+    torch.cuda.profiler.stop()
     barrier()
     ms = max_over_ranks(ms)
     ms_per_step = ms / args.steps
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
     kernel_us = ms_per_step * 1e3 / len(layers)
+
+    if args.kernel_only:   # for profiler runs: nothing but the timed region
+        sampler.stop.set()
+        peak, peak_kind = measured_peaks()
+        achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+        if world > 1:
+            dist.destroy_process_group()
+        return {"metric": "w4a16_linear_hbm_gbs_m1", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+                "steps": args.steps, "ms_per_step": round(ms_per_step, 5), "kernel_only": True,
+                "roofline": {"achieved": round(achieved, 1), "peak": peak, "frac": round(achieved / peak, 4)}} if rank == 0 else {}
 
     # ---- the same K replays with plain stream-ordered launches, for comparison
     plain = None
@@ -505,7 +555,7 @@ def run_product(args) -> dict:
         "gpu_launches": args.steps * len(layers),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "peak_kind": peak_kind, "frac_of_8tbs": round(achieved / 8000, 4),
-                     "traffic": None, "kernel": "linear_mma_kernel", "mean_launch_us": round(kernel_us, 3),
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "kernel": "linear_mma_kernel", "mean_launch_us": round(kernel_us, 3),
                      "bytes_per_launch": step_bytes // len(layers)},
         "clocks": clocks,
     }
@@ -593,8 +643,15 @@ def main() -> None:
                         help="plain stream-ordered launches instead of programmatic dependent launch")
     parser.set_defaults(pdl=True)
     parser.add_argument("--quick", action="store_true", help="skip the per-shape tables")
+    parser.add_argument("--kernel-only", action="store_true",
+                        help="only the timed region (bracketed by cudaProfilerStart/Stop), for profiler runs")
+    parser.add_argument("--single-layer", type=int, nargs=3, metavar=("K", "N", "M"),
+                        help="run --steps launches of one layer shape only (profiling target)")
     args = parser.parse_args()
-    result = run_reference(args) if args.impl == "reference" else run_product(args)
+    if args.single_layer:
+        result = run_single_layer(args)
+    else:
+        result = run_reference(args) if args.impl == "reference" else run_product(args)
     if result:
         print(json.dumps(result), flush=True)
 
