@@ -393,6 +393,107 @@ def run_single_layer(args) -> dict:
             "gbs": round(payload / us / 1e3, 1), "peak": peak, "peak_kind": kind, "bytes_per_launch": payload}
 
 
+def run_tensor_parallel(args) -> dict:
+    """`--workload llama70b_tp`: the seven linears of one Llama-3-70B decoder block, each sharded over the
+    N ranks of this job: q, k, v, o, gate, up column-parallel (rows of W split, all-gather of y) and
+    down row-parallel (K split, all-reduce of FP32 partials).  Total work is fixed, so this is strong
+    scaling; the value is the unsharded layers' algorithmic bytes over the step time (max over ranks).
+    Reported with and without the collectives so their cost is visible.
+    """
+    import torch
+    import torch.distributed as dist
+
+    from nibble_b200.sharded import (ColumnParallelQuantizedLinear, PeerColumnParallelQuantizedLinear,
+                                     PeerRowParallelQuantizedLinear, RowParallelQuantizedLinear)
+
+    peer = args.collective == "p2p"
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1 or "RANK" in os.environ:
+        dist.init_process_group("nccl", device_id=device)
+    else:   # a single process still goes through the same code with a one-rank group
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+    if args.pdl:
+        os.environ["W4A16_PDL"] = "1"
+    m = args.batch
+    order = ["qo_proj", "kv_proj", "kv_proj", "qo_proj", "gate_up_proj", "gate_up_proj", "down_proj"]
+    torch.manual_seed(1234 + rank)
+
+    def shard(name, gather):
+        k, n = LLAMA70B[name]
+        if name == "down_proj":
+            kk = k // world
+            packed = torch.randint(0, 256, (n, kk // 2), dtype=torch.uint8, device=device)
+            scales = (torch.rand((n, kk // GROUP), device=device) * 0.01 + 1e-3).half()
+            if peer and gather:
+                layer = PeerRowParallelQuantizedLinear(packed, scales, GROUP, max_rows=m)
+            else:
+                layer = RowParallelQuantizedLinear(packed, scales, GROUP, input_is_parallel=True)
+            x = torch.randn((m, kk), device=device).half()
+            if not gather:
+                layer = layer.local
+            return layer, x
+        nn = n // world
+        packed = torch.randint(0, 256, (nn, k // 2), dtype=torch.uint8, device=device)
+        scales = (torch.rand((nn, k // GROUP), device=device) * 0.01 + 1e-3).half()
+        if peer and gather:
+            layer = PeerColumnParallelQuantizedLinear(packed, scales, GROUP, max_rows=m)
+        else:
+            layer = ColumnParallelQuantizedLinear(packed, scales, GROUP, gather_output=gather)
+        return layer, torch.randn((m, k), device=device).half()
+
+    def measure(gather: bool) -> float:
+        # three sets of weights so that consecutive steps never re-read a set that is still in L2
+        sets = [[shard(name, gather) for name in order] for _ in range(3)]
+
+        def step():
+            for layers in sets:
+                for layer, x in layers:
+                    layer(x)
+
+        with torch.inference_mode():
+            graph = capture(torch, step)
+            for _ in range(max(args.warmup, 3)):
+                graph.replay()
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            ms = time_replays(torch, graph, args.steps)
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        del graph, sets
+        torch.cuda.empty_cache()
+        return float(t.item()) / args.steps / 3.0   # ms per decoder block
+
+    block_bytes = sum(algorithmic_bytes(m, *LLAMA70B[name]) for name in order)
+    with_collectives = measure(True)
+    kernels_only = measure(False)
+    peak, peak_kind = measured_peaks()
+    result = {
+        "metric": "w4a16_linear_hbm_gbs_tp", "value": round(block_bytes / (with_collectives * 1e-3) / 1e9, 1), "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(with_collectives, 5),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate",
+        "data": "synthetic (random codes and scales)",
+        "config": {"workload": "llama70b_tp", "M": m, "layers_per_step": len(order), "bytes_per_step": block_bytes,
+                   "parallelism": f"tp{world}: column-parallel + all-gather, down_proj row-parallel + all-reduce "
+                                  + ("(kernel-epilogue peer stores over NVLink + flags)" if peer else "(NCCL)"),
+                   "programmatic_launch": bool(args.pdl), "l2_policy": "three weight sets per graph replay"},
+        "kernels_only": {"ms_per_step": round(kernels_only, 5), "value": round(block_bytes / (kernels_only * 1e-3) / 1e9, 1)},
+        "collectives_ms_per_step": round(with_collectives - kernels_only, 5),
+        "roofline": {"bound": "hbm", "achieved": round(block_bytes / (kernels_only * 1e-3) / 1e9 / world, 1),
+                     "peak": peak, "unit": "GB/s per GPU, kernels only", "peak_kind": peak_kind,
+                     "frac": round(block_bytes / (kernels_only * 1e-3) / 1e9 / world / peak, 4), "traffic": None},
+        "gpu_launches": args.steps * 3 * len(order),
+    }
+    dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
 def run_product(args) -> dict:
     import torch
     import torch.distributed as dist
@@ -645,11 +746,18 @@ def main() -> None:
     parser.add_argument("--quick", action="store_true", help="skip the per-shape tables")
     parser.add_argument("--kernel-only", action="store_true",
                         help="only the timed region (bracketed by cudaProfilerStart/Stop), for profiler runs")
+    parser.add_argument("--workload", choices=["tinyllama_decode_linears_m1", "llama70b_tp"],
+                        default="tinyllama_decode_linears_m1")
+    parser.add_argument("--batch", type=int, default=1, help="M for --workload llama70b_tp")
+    parser.add_argument("--collective", choices=["p2p", "nccl"], default="p2p",
+                        help="llama70b_tp: exchange fused into the kernel epilogue (peer stores) or NCCL calls")
     parser.add_argument("--single-layer", type=int, nargs=3, metavar=("K", "N", "M"),
                         help="run --steps launches of one layer shape only (profiling target)")
     args = parser.parse_args()
     if args.single_layer:
         result = run_single_layer(args)
+    elif args.workload == "llama70b_tp" and args.impl == "product":
+        result = run_tensor_parallel(args)
     else:
         result = run_reference(args) if args.impl == "reference" else run_product(args)
     if result:

@@ -95,6 +95,58 @@ int w4a16_linear_f16_config(const void* x, const void* packed, const void* scale
 size_t w4a16_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
 
 /*
+ * Tensor-parallel fan-out (no counterpart in the reference, which is single-GPU).  A layer sharded
+ * over `world` GPUs of one node writes its result straight into a buffer on every GPU from the
+ * kernel epilogue -- plain stores into peer-mapped memory over NVLink -- instead of handing it to a
+ * collective library afterwards.  `outputs[r]` is where this rank's elements go on rank r (element
+ * (m, n) lands at outputs[r][m * ld + column_offset + n]; FP16, or FP32 with W4A16_FLAG_OUTPUT_F32).
+ * When every store of the launch is visible system-wide the kernel increments *send_epoch and writes
+ * the new value to flags[r][rank] on every rank.  With wait_polls > 0 the launch then also waits, at
+ * most that many polls per sender, until every rank has published the same epoch in this rank's
+ * flags, so that its completion means "the gathered result is here"; a sender that never arrives is
+ * recorded as sender + 1 in *status instead of hanging the GPU.  All pointer arrays and counters are
+ * device memory; `done_counter`, `send_epoch` and `status` are single words owned by this layer on
+ * this rank, zero at start.  Every rank must issue the same sequence of launches for a layer.
+ * Column-parallel layers use it as an all-gather (ld = full N, column_offset = rank * N_local);
+ * row-parallel layers push FP32 partials (outputs[r] = staging[r] + rank * M * N) and finish with
+ * w4a16_sum_partials_f16.  Peer memory must be mapped by the caller (CUDA IPC, cuMem, or torch's
+ * symmetric memory).
+ */
+typedef struct w4a16_peer_target {
+    void* const* outputs;
+    uint32_t* const* flags;
+    uint32_t* done_counter;
+    uint32_t* send_epoch;
+    uint32_t* status;
+    int64_t ld;
+    int64_t column_offset;
+    int64_t wait_polls;
+    int32_t rank;
+    int32_t world;
+} w4a16_peer_target;
+
+/* w4a16_linear_f16 whose result goes to every rank described by `peers` (fast path only: group 128,
+ * aligned pointers; otherwise W4A16_ERR_BAD_CONFIG).  y of the plain entry point is not written. */
+int w4a16_linear_f16_peers(const void* x, const void* packed, const void* scales,
+                           int64_t M, int64_t N, int64_t K, int64_t group_size,
+                           void* workspace, size_t workspace_bytes, uint32_t flags,
+                           const w4a16_peer_target* peers, w4a16_stream_t stream);
+
+/* Enqueues a one-warp kernel that waits until flags[r] has reached *wait_epoch + 1 for every
+ * r < world, then stores that value to *wait_epoch.  The wait is bounded: after max_polls polls
+ * (about 40 ns apart) of a sender that never arrives it gives up and records sender + 1 in *status
+ * (device word, zero while healthy), so a missing rank ends in an error the host can read, not a hang. */
+int w4a16_wait_peers(const uint32_t* flags, uint32_t* wait_epoch, int32_t world, uint32_t* status,
+                     int64_t max_polls, w4a16_stream_t stream);
+
+/* y[i] = half(sum_r partials[r * count + i]), r ascending: the finish of a row-parallel layer.
+ * With `flags` non-NULL every block first waits (at most max_polls polls per sender) until flags[r]
+ * has reached *epoch for all r < world, reporting a missing sender in *status as above. */
+int w4a16_sum_partials_f16(const void* partials, void* y, int64_t count, int32_t world,
+                           const uint32_t* flags, const uint32_t* epoch, uint32_t* status, int64_t max_polls,
+                           w4a16_stream_t stream);
+
+/*
  * packed + scales -> FP16 [N, K], bit-identical to half(float(code) * float(scale)).
  * Replaces the reference's int4_dequantize_cuda (csrc/int4_linear_kernel.cu:805-867).
  * Requires group_size a positive multiple of 32 and `packed` 16-byte aligned, as the reference does.

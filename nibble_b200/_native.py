@@ -28,6 +28,23 @@ class LinearConfig(ctypes.Structure):
     ]
 
 
+class PeerTarget(ctypes.Structure):
+    """Mirror of ``w4a16_peer_target``: where a sharded layer's result goes on every rank."""
+
+    _fields_ = [
+        ("outputs", ctypes.c_void_p),
+        ("flags", ctypes.c_void_p),
+        ("done_counter", ctypes.c_void_p),
+        ("send_epoch", ctypes.c_void_p),
+        ("status", ctypes.c_void_p),
+        ("ld", ctypes.c_int64),
+        ("column_offset", ctypes.c_int64),
+        ("wait_polls", ctypes.c_int64),
+        ("rank", ctypes.c_int32),
+        ("world", ctypes.c_int32),
+    ]
+
+
 _P = ctypes.c_void_p
 _I = ctypes.c_int64
 
@@ -41,6 +58,12 @@ C_API = {
     "w4a16_linear_workspace_bytes": (ctypes.c_size_t, [_I, _I, _I]),
     "w4a16_linear_f16_static_scratch": (ctypes.c_int, [_P, _P, _P, _P, _I, _I, _I, _I, ctypes.c_uint32, _P]),
     "w4a16_static_scratch_bytes": (ctypes.c_size_t, []),
+    "w4a16_linear_f16_peers": (
+        ctypes.c_int,
+        [_P, _P, _P, _I, _I, _I, _I, _P, ctypes.c_size_t, ctypes.c_uint32, ctypes.POINTER(PeerTarget), _P],
+    ),
+    "w4a16_wait_peers": (ctypes.c_int, [_P, _P, ctypes.c_int32, _P, _I, _P]),
+    "w4a16_sum_partials_f16": (ctypes.c_int, [_P, _P, _I, ctypes.c_int32, _P, _P, _P, _I, _P]),
     "w4a16_dequantize_f16": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
     "w4a16_launch_count": (ctypes.c_uint64, []),
     "w4a16_status_string": (ctypes.c_char_p, [ctypes.c_int]),
@@ -49,6 +72,7 @@ C_API = {
 
 FLAG_PROGRAMMATIC_LAUNCH = 1 << 0
 FLAG_FORCE_GENERIC = 1 << 1
+FLAG_OUTPUT_F32 = 1 << 2
 
 
 @functools.lru_cache(maxsize=None)

@@ -117,6 +117,49 @@ int w4a16_linear_f16_config(const void* x, const void* packed, const void* scale
                                     (flags & W4A16_FLAG_OUTPUT_F32) != 0, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int w4a16_linear_f16_peers(const void* x, const void* packed, const void* scales, int64_t M, int64_t N, int64_t K,
+                           int64_t group_size, void* workspace, size_t workspace_bytes, uint32_t flags,
+                           const w4a16_peer_target* peers, w4a16_stream_t stream) {
+    if (peers == nullptr) return W4A16_ERR_NULL_POINTER;
+    const int status = validate_linear(x, packed, scales, peers, M, N, K, group_size);
+    if (status != W4A16_OK) return status;
+    if (M == 0 || N == 0 || K == 0) return W4A16_ERR_BAD_SHAPE;
+    if (!fast_path_applies(x, packed, K, group_size)) return W4A16_ERR_BAD_CONFIG;
+    w4a16::LinearProblem p{static_cast<const __half*>(x), static_cast<const uint8_t*>(packed),
+                           static_cast<const __half*>(scales), nullptr, M, N, K, group_size,
+                           workspace, workspace_bytes, peers};
+    int max_splits = 1;
+    if (workspace != nullptr && aligned16(workspace)) {
+        for (int splits = w4a16::kMaxKSplits; splits > 1; splits >>= 1) {
+            if (workspace_bytes >= w4a16::linear_workspace_bytes_for(M, N, splits)) {
+                max_splits = splits;
+                break;
+            }
+        }
+    }
+    w4a16_linear_config cfg = w4a16::choose_linear_config(M, N, K, max_splits);
+    if (reinterpret_cast<uintptr_t>(scales) % 4 != 0) cfg.unroll = 1;
+    return w4a16::launch_linear_mma(p, cfg, (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0,
+                                    (flags & W4A16_FLAG_OUTPUT_F32) != 0, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int w4a16_wait_peers(const uint32_t* flags, uint32_t* wait_epoch, int32_t world, uint32_t* status, int64_t max_polls,
+                     w4a16_stream_t stream) {
+    if (flags == nullptr || wait_epoch == nullptr || status == nullptr) return W4A16_ERR_NULL_POINTER;
+    if (max_polls <= 0) return W4A16_ERR_BAD_SHAPE;
+    return w4a16::launch_wait_peers(flags, wait_epoch, world, status, max_polls, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int w4a16_sum_partials_f16(const void* partials, void* y, int64_t count, int32_t world, const uint32_t* flags,
+                           const uint32_t* epoch, uint32_t* status, int64_t max_polls, w4a16_stream_t stream) {
+    if (count < 0 || world < 1 || world > 32) return W4A16_ERR_BAD_SHAPE;
+    if (count == 0) return W4A16_OK;
+    if (partials == nullptr || y == nullptr) return W4A16_ERR_NULL_POINTER;
+    if (flags != nullptr && (epoch == nullptr || status == nullptr || max_polls <= 0)) return W4A16_ERR_NULL_POINTER;
+    return w4a16::launch_sum_partials(static_cast<const float*>(partials), static_cast<__half*>(y), count, world, flags,
+                                      epoch, status, max_polls, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int w4a16_dequantize_f16(const void* packed, const void* scales, void* weights, int64_t N, int64_t K,
                          int64_t group_size, w4a16_stream_t stream) {
     if (N < 0 || K < 0 || (K & 1)) return W4A16_ERR_BAD_SHAPE;

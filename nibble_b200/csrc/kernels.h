@@ -27,6 +27,7 @@ struct LinearProblem {
     int64_t M, N, K, group;
     void* workspace;          // may be null
     size_t workspace_bytes;
+    const w4a16_peer_target* peers = nullptr;   // fan the result out to a tensor-parallel group
 };
 
 // Workspace layout for split-K: arrival counters first, FP32 partials after them.
@@ -43,6 +44,13 @@ int launch_linear_mma(const LinearProblem& p, const w4a16_linear_config& cfg, bo
 
 // Any even group size, any alignment, any M.
 int launch_linear_generic(const LinearProblem& p, bool out_f32, cudaStream_t stream);
+
+// Tensor-parallel helpers: bounded wait for every rank's publication, and the rank-ordered sum of
+// FP32 partials into FP16.
+int launch_wait_peers(const unsigned* flags, unsigned* wait_epoch, int world, unsigned* status, long long max_polls,
+                      cudaStream_t stream);
+int launch_sum_partials(const float* partials, __half* y, int64_t count, int world, const unsigned* flags,
+                        const unsigned* epoch, unsigned* status, long long max_polls, cudaStream_t stream);
 
 int launch_dequantize(const uint8_t* packed, const __half* scales, __half* weights, int64_t N,
                       int64_t K, int64_t group, cudaStream_t stream);

@@ -64,7 +64,36 @@ struct MmaParams {
     int k_splits;
     int row_tiles_total;   // ceil(N / (16 * TILES))
     int out_f32;
+    // Optional fan-out of the result to every GPU of a tensor-parallel group (null: plain y).
+    void* const* peer_out;          // [world] where this rank's results go on each rank
+    unsigned* const* peer_flags;    // [world] each rank's arrival flags, indexed by sender
+    unsigned* done_counter;         // CTAs of this launch that finished; left at zero
+    unsigned* send_epoch;           // launches published so far by this layer on this rank
+    unsigned* peer_status;          // zero while healthy; sender + 1 when a wait gave up on a sender
+    long long ld_out;               // elements between batch rows of the peers' buffers
+    long long col_out;              // first column this rank writes there
+    long long wait_polls;           // > 0: also wait (bounded) for every rank's publication of this epoch
+    int rank, world;
 };
+
+// Bounded wait until flags[sender] has reached `epoch` for every sender; a sender that never arrives
+// is recorded in *status (sender + 1) and the wait moves on.
+__device__ __forceinline__ void wait_for_senders(const unsigned* flags, int world, unsigned epoch,
+                                                 long long max_polls, unsigned* status) {
+    for (int sender = 0; sender < world; ++sender) {
+        bool arrived = false;
+        for (long long poll = 0; poll < max_polls; ++poll) {
+            unsigned seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + sender) : "memory");
+            if (static_cast<int>(seen - epoch) >= 0) {
+                arrived = true;
+                break;
+            }
+            __nanosleep(32);
+        }
+        if (!arrived) atomicMax(status, static_cast<unsigned>(sender) + 1u);
+    }
+}
 
 __device__ __forceinline__ void group_barrier(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -432,6 +461,27 @@ linear_mma_kernel(const MmaParams p) {
     const int gthread = kw * 32 + lane;   // thread index inside the group
     const bool split_k = p.k_splits > 1;
 
+    // Final destination of one output element: this rank's y, or the same position in the result
+    // buffer of every rank of the group (plain stores over NVLink into peer-mapped memory).
+    auto write_out = [&](int row, size_t m, float sum) {
+        if (p.peer_out == nullptr) {
+            if (p.out_f32) {
+                static_cast<float*>(p.y)[m * p.N + row] = sum;
+            } else {
+                static_cast<__half*>(p.y)[m * p.N + row] = __float2half_rn(sum);
+            }
+        } else {
+            const size_t at = m * static_cast<size_t>(p.ld_out) + static_cast<size_t>(p.col_out) + row;
+            for (int peer = 0; peer < p.world; ++peer) {
+                if (p.out_f32) {
+                    static_cast<float*>(p.peer_out[peer])[at] = sum;
+                } else {
+                    static_cast<__half*>(p.peer_out[peer])[at] = __float2half_rn(sum);
+                }
+            }
+        }
+    };
+
     // Combines the group's warps for one finished row tile and writes it out (or hands it to the
     // split-K reduction); leaves `total` cleared for the next tile.
     auto finish_tile = [&](int tile) {
@@ -441,10 +491,8 @@ linear_mma_kernel(const MmaParams p) {
         auto store = [&](int row, size_t m, float sum) {
             if (split_k) {
                 p.partial[(static_cast<size_t>(split) * p.M + m) * p.N + row] = sum;
-            } else if (p.out_f32) {
-                static_cast<float*>(p.y)[m * p.N + row] = sum;
             } else {
-                static_cast<__half*>(p.y)[m * p.N + row] = __float2half_rn(sum);
+                write_out(row, m, sum);
             }
         };
         if constexpr (KW > 1) {
@@ -509,11 +557,7 @@ linear_mma_kernel(const MmaParams p) {
                     for (int s = 0; s < p.k_splits; ++s) {
                         sum += __ldcg(p.partial + (static_cast<size_t>(s) * p.M + m) * p.N + row);
                     }
-                    if (p.out_f32) {
-                        static_cast<float*>(p.y)[m * p.N + row] = sum;
-                    } else {
-                        static_cast<__half*>(p.y)[m * p.N + row] = __float2half_rn(sum);
-                    }
+                    write_out(row, m, sum);
                 }
                 if (gthread == 0) *counter = 0u;   // ready for the next call sharing the workspace
             }
@@ -524,8 +568,6 @@ linear_mma_kernel(const MmaParams p) {
     if (steps_per_tile == 0) {
         // A warp without a share of K still meets its group at every tile's barrier.
         for (int tile = first_tile; tile < p.row_tiles_total; tile += tile_stride) finish_tile(tile);
-        cp_async_wait<0>();
-        return;
     }
 
     if (steps_left > 0) {
@@ -605,6 +647,70 @@ linear_mma_kernel(const MmaParams p) {
         }
     }
     cp_async_wait<0>();   // nothing of this thread may still be landing in shared memory at exit
+
+    if (p.peer_out != nullptr) {
+        // Publish: once every CTA of the launch has made its peer stores visible system-wide, the
+        // last one to finish bumps this layer's epoch and writes it to flags[rank] on every rank.
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence_system();
+            const unsigned ctas = gridDim.x * gridDim.y * gridDim.z;
+            if (atomicAdd(p.done_counter, 1u) == ctas - 1) {
+                *p.done_counter = 0u;
+                const unsigned epoch = *p.send_epoch + 1u;
+                *p.send_epoch = epoch;
+                __threadfence_system();
+                for (int peer = 0; peer < p.world; ++peer) {
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[peer] + p.rank), "r"(epoch)
+                                 : "memory");
+                }
+                // Optionally the launch itself completes only when every rank's part has landed here.
+                if (p.wait_polls > 0) {
+                    wait_for_senders(p.peer_flags[p.rank], p.world, epoch, p.wait_polls, p.peer_status);
+                }
+            }
+        }
+    }
+}
+
+// Waits (bounded) until every rank has published at least the epoch this rank expects next for the
+// layer, i.e. until all slices of the gathered result have landed in this rank's buffer.
+__global__ void wait_peers_kernel(const unsigned* flags, unsigned* wait_epoch, int world, unsigned* status,
+                                  long long max_polls) {
+    const int lane = threadIdx.x;
+    const unsigned expected = *wait_epoch + 1u;
+    bool ok = true;
+    if (lane < world) {
+        ok = false;
+        for (long long poll = 0; poll < max_polls; ++poll) {
+            unsigned seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + lane) : "memory");
+            if (static_cast<int>(seen - expected) >= 0) {
+                ok = true;
+                break;
+            }
+            __nanosleep(40);
+        }
+        if (!ok) atomicMax(status, static_cast<unsigned>(lane) + 1u);   // which sender never arrived
+    }
+    __syncwarp();
+    if (lane == 0) *wait_epoch = expected;
+}
+
+// y = half(sum over ranks of partials[rank]), summed in rank order so every rank gets identical bits.
+// With `flags` the block first waits (bounded) until every rank has published *epoch.
+__global__ void sum_partials_kernel(const float* __restrict__ partials, __half* __restrict__ y, long long count,
+                                    int world, const unsigned* flags, const unsigned* epoch, unsigned* status,
+                                    long long max_polls) {
+    if (flags != nullptr) {
+        if (threadIdx.x == 0) wait_for_senders(flags, world, *epoch, max_polls, status);
+        __syncthreads();
+    }
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    float sum = 0.f;
+    for (int r = 0; r < world; ++r) sum += __ldcg(partials + static_cast<long long>(r) * count + i);
+    y[i] = __float2half_rn(sum);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -769,6 +875,28 @@ w4a16_linear_config choose_linear_config(int64_t M, int64_t N, int64_t K, int ma
     return c;
 }
 
+int launch_wait_peers(const unsigned* flags, unsigned* wait_epoch, int world, unsigned* status, long long max_polls,
+                      cudaStream_t stream) {
+    if (world < 1 || world > 32) return W4A16_ERR_BAD_SHAPE;
+    wait_peers_kernel<<<1, 32, 0, stream>>>(flags, wait_epoch, world, status, max_polls);
+    if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    return W4A16_OK;
+}
+
+int launch_sum_partials(const float* partials, __half* y, int64_t count, int world, const unsigned* flags,
+                        const unsigned* epoch, unsigned* status, long long max_polls, cudaStream_t stream) {
+    if (count <= 0) return W4A16_OK;
+    const int threads = 256;
+    const int64_t blocks = (count + threads - 1) / threads;
+    if (blocks > INT32_MAX) return W4A16_ERR_TOO_LARGE;
+    sum_partials_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(partials, y, count, world, flags, epoch,
+                                                                               status, max_polls);
+    if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    return W4A16_OK;
+}
+
 int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_in, bool programmatic,
                       bool out_f32, cudaStream_t stream) {
     if (prob.group != kGroup || prob.K % kGroup != 0) return W4A16_ERR_BAD_CONFIG;
@@ -819,6 +947,34 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
     params.k_splits = splits;
     params.row_tiles_total = static_cast<int>((prob.N + 16 * cfg.row_tiles - 1) / (16 * cfg.row_tiles));
     params.out_f32 = out_f32 ? 1 : 0;
+    params.peer_out = nullptr;
+    params.peer_flags = nullptr;
+    params.done_counter = nullptr;
+    params.send_epoch = nullptr;
+    params.peer_status = nullptr;
+    params.wait_polls = 0;
+    params.ld_out = 0;
+    params.col_out = 0;
+    params.rank = 0;
+    params.world = 1;
+    if (prob.peers != nullptr) {
+        const w4a16_peer_target& t = *prob.peers;
+        if (t.outputs == nullptr || t.flags == nullptr || t.done_counter == nullptr || t.send_epoch == nullptr ||
+            t.world < 1 || t.world > 32 || t.rank < 0 || t.rank >= t.world || t.ld < prob.N || t.column_offset < 0) {
+            return W4A16_ERR_BAD_SHAPE;
+        }
+        params.peer_out = t.outputs;
+        params.peer_flags = t.flags;
+        params.done_counter = t.done_counter;
+        params.send_epoch = t.send_epoch;
+        if (t.wait_polls > 0 && t.status == nullptr) return W4A16_ERR_NULL_POINTER;
+        params.peer_status = t.status;
+        params.wait_polls = t.wait_polls;
+        params.ld_out = t.ld;
+        params.col_out = t.column_offset;
+        params.rank = t.rank;
+        params.world = t.world;
+    }
     if (splits > 1) {
         const size_t need = linear_workspace_bytes_for(prob.M, prob.N, splits);
         if (prob.workspace == nullptr || prob.workspace_bytes < need) return W4A16_ERR_WORKSPACE;

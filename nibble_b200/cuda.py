@@ -40,6 +40,28 @@ else:
     _EXTENSION_LOAD_ERROR = None
 
 
+def set_programmatic_launch(enabled: bool) -> None:
+    """Turn programmatic dependent launch of the fused kernel on or off for this process.
+
+    With it on, a fused-linear kernel may start and prefetch packed weights and scales while the
+    previous kernel of the stream is still finishing; it waits for that kernel before reading its
+    activations or writing its output.  Only valid while no kernel that may still be running writes
+    the weights or scales, i.e. for inference with weights already in place.  Off by default.
+    """
+    import os
+
+    if enabled:
+        os.environ["W4A16_PDL"] = "1"
+    else:
+        os.environ.pop("W4A16_PDL", None)
+
+
+def programmatic_launch_enabled() -> bool:
+    import os
+
+    return os.environ.get("W4A16_PDL") == "1"
+
+
 def cuda_extension_available() -> bool:
     """True when the compiled operator library loaded."""
     return _EXTENSION_LOAD_ERROR is None
