@@ -52,7 +52,9 @@ enum {
     W4A16_FLAG_FORCE_GENERIC = 1u << 1,
     /* y is float [M, N] and receives the unrounded FP32 sums: for K-sharded layers whose partial
      * results are added across devices before the single rounding to FP16. */
-    W4A16_FLAG_OUTPUT_F32 = 1u << 2
+    W4A16_FLAG_OUTPUT_F32 = 1u << 2,
+    /* Keep batches of 65 rows and more on the mma.sync kernel instead of the tcgen05 GEMM (A/B, tests). */
+    W4A16_FLAG_NO_TCGEN05 = 1u << 3
 };
 
 /* Explicit launch shape of the fused tensor-core kernel; zero fields mean "choose for me". */
@@ -70,8 +72,11 @@ typedef struct w4a16_linear_config {
  * Replaces the reference's int4_linear_cuda (csrc/int4_linear_kernel.cu:641-802) and the kernels
  * it dispatches to (decode_multirow :325-404, small_batch :542-617, naive :20-69).
  *
- * Fast path (tensor-core kernel) when group_size == 128 and x, packed are 16-byte aligned;
- * otherwise a generic kernel that accepts any even group_size and any alignment.
+ * Fast path when group_size == 128 and x, packed are 16-byte aligned: M <= 64 runs the mma.sync
+ * streaming kernel, larger M a tcgen05 GEMM whose producer warps dequantise into the operand tiles
+ * (no FP16 weight matrix in memory; weights enter the product as half(code * scale), the arithmetic of
+ * the reference's dequantise-then-matmul prefill route, w4a16/linear.py:132-152).
+ * Otherwise a generic kernel that accepts any even group_size and any alignment.
  * `workspace` may be NULL (then K is never split across CTAs); if given it must be 16-byte aligned,
  * hold at least w4a16_linear_workspace_bytes(M, N, K) bytes, be zero-filled before its first use
  * and not be shared by calls that may run concurrently.  The library leaves it ready for re-use.
@@ -173,6 +178,11 @@ int w4a16_linear_f16_static_scratch(const void* x, const void* packed, const voi
 
 /* Size in bytes of the built-in scratch array used by w4a16_linear_f16_static_scratch. */
 size_t w4a16_static_scratch_bytes(void);
+
+/* Device-side health word of the tcgen05 kernel: 0 while healthy; non-zero identifies a barrier wait
+ * that gave up after its spin limit (the kernel then still ran to completion of its clean-up, with an
+ * unfinished result).  Reading synchronises the device and clears the word.  No reference counterpart. */
+int w4a16_device_status(uint32_t* value);
 
 /* Number of kernels this library has launched in this process (all entry points, all devices). */
 uint64_t w4a16_launch_count(void);

@@ -76,6 +76,10 @@ int w4a16_linear_f16(const void* x, const void* packed, const void* scales, void
     if ((flags & W4A16_FLAG_FORCE_GENERIC) || !fast_path_applies(x, packed, K, group_size)) {
         return w4a16::launch_linear_generic(p, out_f32, s);
     }
+    // Prefill-sized batches: dense enough for the tcgen05 tensor cores.
+    if (M >= w4a16::kTcgen05MinRows && !out_f32 && !(flags & W4A16_FLAG_NO_TCGEN05)) {
+        return w4a16::launch_linear_tcgen05(p, s);
+    }
     // Split K across CTAs only as far as the caller's workspace allows.
     int max_splits = 1;
     if (workspace != nullptr && aligned16(workspace)) {
@@ -158,6 +162,14 @@ int w4a16_sum_partials_f16(const void* partials, void* y, int64_t count, int32_t
     if (flags != nullptr && (epoch == nullptr || status == nullptr || max_polls <= 0)) return W4A16_ERR_NULL_POINTER;
     return w4a16::launch_sum_partials(static_cast<const float*>(partials), static_cast<__half*>(y), count, world, flags,
                                       epoch, status, max_polls, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int w4a16_device_status(uint32_t* value) {
+    if (value == nullptr) return W4A16_ERR_NULL_POINTER;
+    unsigned v = 0;
+    const int status = w4a16::read_tcgen05_status(&v);
+    *value = v;
+    return status;
 }
 
 int w4a16_dequantize_f16(const void* packed, const void* scales, void* weights, int64_t N, int64_t K,

@@ -42,6 +42,12 @@ w4a16_linear_config choose_linear_config(int64_t M, int64_t N, int64_t K, int ma
 int launch_linear_mma(const LinearProblem& p, const w4a16_linear_config& cfg, bool programmatic,
                       bool out_f32, cudaStream_t stream);
 
+// Prefill-sized batches: dequantisation fused into a tcgen05 GEMM (group == 128, aligned x / packed).
+int launch_linear_tcgen05(const LinearProblem& p, cudaStream_t stream);
+// Status word of that kernel (non-zero: a bounded barrier wait gave up); reading clears it and synchronises.
+int read_tcgen05_status(unsigned* value);
+constexpr int kTcgen05MinRows = 65;     // smaller batches stay on the mma.sync kernel
+
 // Any even group size, any alignment, any M.
 int launch_linear_generic(const LinearProblem& p, bool out_f32, cudaStream_t stream);
 

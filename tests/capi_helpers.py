@@ -52,7 +52,7 @@ def capi_dequantize(packed, scales, group_size=128, expect=0):
 
 
 def check_against_oracle(y: torch.Tensor, x: torch.Tensor, packed: torch.Tensor, scales: torch.Tensor,
-                         group_size: int = 128, rows=None) -> float:
+                         group_size: int = 128, rows=None, fp16_weights: bool = False) -> float:
     """Both acceptance criteria for the fused linear, on the same packed codes:
 
     * ``|y - fp64(dequantize-then-matmul)| <= 1e-2 * ||x_m||_2 * max|w|`` for every output, and
@@ -60,6 +60,9 @@ def check_against_oracle(y: torch.Tensor, x: torch.Tensor, packed: torch.Tensor,
       reference's CUDA tests use).
 
     ``rows`` restricts the check to a subset of output rows (outputs are independent per row).
+    ``fp16_weights`` makes the second comparison against the product with the dequantised weights
+    rounded to FP16 first, which is what the reference computes for batches above its fused limit
+    (dequantise, then ``F.linear``; w4a16/linear.py:132-190) and what the prefill kernel computes.
     Returns the largest error as a fraction of the bound.
     """
     xs = x.cpu().numpy()
@@ -75,6 +78,10 @@ def check_against_oracle(y: torch.Tensor, x: torch.Tensor, packed: torch.Tensor,
     err = np.abs(got.numpy().astype(np.float64) - exact)
     worst = float((err / np.maximum(bound, 1e-30)).max()) if err.size else 0.0
     assert (err <= bound).all(), f"max error {err.max():.4g} exceeds bound (ratio {worst:.3f})"
-    expected = torch.from_numpy(oracle.linear_reference(xs, p, s, group_size))
+    if fp16_weights:
+        w16 = oracle.dequantize_weights(p, s, group_size).astype(np.float16).astype(np.float32)
+        expected = torch.from_numpy((xs.astype(np.float32) @ w16.T).astype(np.float16))
+    else:
+        expected = torch.from_numpy(oracle.linear_reference(xs, p, s, group_size))
     torch.testing.assert_close(got, expected, rtol=1e-2, atol=1e-2)
     return worst
