@@ -1,5 +1,5 @@
 // Prefill-sized W4A16 linear on the 5th-generation tensor cores: packed INT4 weights are
-// dequantised by the producer warps straight into the swizzled shared-memory operand layout of
+// dequantised by producer warps straight into the swizzled shared-memory operand layout of
 // tcgen05.mma, so the FP16 weight matrix is never written to (or re-read from) HBM.
 //
 // Replaces, for large M, the reference's dequantise-to-FP16-then-cuBLAS route
@@ -9,19 +9,28 @@
 //
 //   D[128 x BN] (TMEM, FP32)  +=  A[128 x 64] (W rows, K-major, SWIZZLE_128B)  x  B[BN x 64] (x rows, K-major)
 //
-// so the output channels sit on the MMA's M axis and the batch on its N axis; the epilogue writes
-// the transposed tile back as y[m][n].
+// The output channels sit on the MMA's M axis (TMEM lanes) and the batch on its N axis (TMEM
+// columns, BN a multiple of 16 up to 256 chosen per call), so one pass of dequantisation feeds up to
+// 256 batch rows.
 //
-// CTA = 5 warps.  Warps 0-3: one thread per weight row -- load 32 packed bytes per 64-wide K block,
-// unpack, scale, re-pair to memory order and store eight 16-byte pieces at their swizzled places;
-// the same threads copy the x tile with cp.async.  Warp 4: allocates TMEM, and one of its lanes issues
-// the MMAs and the commits that recycle pipeline stages.  After the last K block warps 0-3 read the
-// accumulator with tcgen05.ld and store FP16.
+// Persistent CTAs, one per SM, each walking a strided list of output tiles; 14 warps with fixed roles:
+//   warp 0      one lane issues the TMA loads of the x tile (tensor map built per call on the host)
+//   warp 1      allocates TMEM; one lane issues the MMAs and the commits that recycle pipeline stages
+//   warps 2-5   epilogue: tcgen05.ld the accumulator of the finished tile, round to FP16, store
+//   warps 6-13  dequantisers: two threads per weight row, 32 codes each per 64-wide K block ->
+//               unpack, scale, re-pair to memory order, four 16-byte stores at their swizzled places
+// The accumulator is double buffered (2 x 256 TMEM columns), so the epilogue of one tile runs under
+// the main loop of the next.
 //
 // Every wait on an mbarrier is bounded; a wait that gives up sets a device status word and the CTA
 // still runs to its TMEM deallocation, so a logic error ends in a reported failure, not a hung GPU.
+// A give-up always follows a wait far longer than a bulk copy takes, so no copy is in flight when
+// the CTA leaves.
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+
+#include <algorithm>
 
 #include "kernels.h"
 #include "unpack.cuh"
@@ -29,13 +38,19 @@
 namespace w4a16 {
 namespace {
 
-constexpr int kBM = 128;          // output channels per CTA (MMA M)
-constexpr int kBN = 128;          // batch rows per CTA (MMA N)
+constexpr int kBM = 128;          // output channels per tile (MMA M)
+constexpr int kMaxBN = 256;       // batch rows per tile at most (MMA N)
 constexpr int kBK = 64;           // K per pipeline stage: one 128-byte swizzle row of FP16
 constexpr int kStagesTc = 4;
-constexpr int kTileBytes = kBM * kBK * 2;                 // 16 KB, A and B tiles alike (kBM == kBN)
-constexpr int kProducerThreads = 128;
-constexpr int kThreadsTc = kProducerThreads + 32;
+constexpr int kATileBytes = kBM * kBK * 2;        // 16 KB
+constexpr int kBTileBytes = kMaxBN * kBK * 2;     // 32 KB
+constexpr int kStageBytes = kATileBytes + kBTileBytes;
+constexpr int kDequantThreads = 256;
+constexpr int kEpilogueThreads = 128;
+constexpr int kFirstDequantWarp = 6;
+constexpr int kThreadsTc = (kFirstDequantWarp + kDequantThreads / 32) * 32;   // 448
+constexpr int kTmemColumns = 2 * kMaxBN;
+constexpr int kGroupM = 4;        // batch tiles walked together before moving along N
 constexpr unsigned kSpinLimit = 1u << 20;
 
 // Set when a bounded wait inside the tensor-core kernel gives up (which barrier: low byte).
@@ -50,6 +65,9 @@ __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
 }
 __device__ __forceinline__ void mbar_arrive(unsigned bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 // Bounded wait for the phase with the given parity to complete.  False (and a status code) on give-up.
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, unsigned code) {
@@ -79,15 +97,13 @@ __device__ __forceinline__ uint64_t operand_desc(unsigned smem_address) {
     return desc;
 }
 
-// Instruction descriptor: FP32 accumulate, FP16 A and B, both K-major, N = kBN, M = 128.
-constexpr uint32_t kInstrDesc = (1u << 4) | (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
-
-__device__ __forceinline__ void umma_f16(unsigned tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_f16(unsigned tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t instr_desc,
+                                         uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(kInstrDesc), "r"(accumulate)
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(instr_desc), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(unsigned bar) {
@@ -95,43 +111,59 @@ __device__ __forceinline__ void umma_commit(unsigned bar) {
 }
 
 struct TcParams {
-    const __half* x;
     const uint8_t* packed;
     const __half* scales;
     __half* y;
     int M, N, K;
+    int bn;            // batch rows per tile (multiple of 16)
+    int m_tiles, n_tiles, total_tiles;
 };
 
+// Tiles are numbered so that kGroupM batch tiles sharing one slab of weights are adjacent: CTAs
+// running at the same time then read a small set of x tiles and weight slabs out of L2.
+__device__ __forceinline__ void tile_coords(int tile, const TcParams& p, int& m_tile, int& n_tile) {
+    const int per_group = kGroupM * p.n_tiles;
+    const int g = tile / per_group;
+    const int first = g * kGroupM;
+    const int gm = min(kGroupM, p.m_tiles - first);
+    const int local = tile - g * per_group;
+    n_tile = local / gm;
+    m_tile = first + (local - n_tile * gm);
+}
+
 __global__ void __launch_bounds__(kThreadsTc, 1)
-linear_tcgen05_kernel(const TcParams p) {
+linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte aligned tiles (the swizzle pattern is a function of address bits 4-9)
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const unsigned a_tiles = base;
-    const unsigned b_tiles = base + kStagesTc * kTileBytes;
-    const unsigned bars = b_tiles + kStagesTc * kTileBytes;      // full[stages], empty[stages], done
-    const unsigned tmem_slot = bars + (2 * kStagesTc + 1) * 8;
+    auto a_tile = [&](int s) { return base + s * kStageBytes; };
+    auto b_tile = [&](int s) { return base + s * kStageBytes + kATileBytes; };
+    const unsigned bars = base + kStagesTc * kStageBytes;
     auto full_bar = [&](int s) { return bars + s * 8; };
     auto empty_bar = [&](int s) { return bars + (kStagesTc + s) * 8; };
-    const unsigned done_bar = bars + 2 * kStagesTc * 8;
+    auto acc_full_bar = [&](int b) { return bars + (2 * kStagesTc + b) * 8; };
+    auto acc_empty_bar = [&](int b) { return bars + (2 * kStagesTc + 2 + b) * 8; };
+    const unsigned tmem_slot = bars + (2 * kStagesTc + 4) * 8;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const int n0 = blockIdx.x * kBM;
-    const int m0 = blockIdx.y * kBN;
     const int k_blocks = p.K / kBK;
 
     if (tid == 0) {
         for (int s = 0; s < kStagesTc; ++s) {
-            mbar_init(full_bar(s), kProducerThreads);
-            mbar_init(empty_bar(s), 1);
+            mbar_init(full_bar(s), kDequantThreads + 1);   // every dequantiser thread + the TMA issuer
+            mbar_init(empty_bar(s), 1);                    // one tcgen05.commit
         }
-        mbar_init(done_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_empty_bar(b), kEpilogueThreads);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&x_map)) : "memory");
     }
-    if (warp == 4) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kBN) : "memory");
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemColumns) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -141,104 +173,171 @@ linear_tcgen05_kernel(const TcParams p) {
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
     bool healthy = true;
-    if (warp < 4) {
-        // ---------------- producers: thread r owns weight row n0 + r and batch row m0 + r ----------
-        const int r = tid;
-        const int w_row = min(n0 + r, p.N - 1);
-        const int x_row = min(m0 + r, p.M - 1);
-        const uint8_t* w_ptr = p.packed + static_cast<size_t>(w_row) * (p.K >> 1);
-        const __half* s_ptr = p.scales + static_cast<size_t>(w_row) * (p.K / kGroup);
-        const __half* x_ptr = p.x + static_cast<size_t>(x_row) * p.K;
-        const unsigned row_offset = (r >> 3) * 1024 + (r & 7) * 128;   // this row inside a tile
-        const unsigned swz = r & 7;
-        for (int kb = 0; kb < k_blocks && healthy; ++kb) {
-            const int stage = kb % kStagesTc;
-            const unsigned round = kb / kStagesTc;
-            if (round > 0) healthy = mbar_wait(empty_bar(stage), (round - 1) & 1, 0x10u + stage);
-            if (!healthy) break;
-            const unsigned a_row = a_tiles + stage * kTileBytes + row_offset;
-            const unsigned b_row = b_tiles + stage * kTileBytes + row_offset;
-            // x tile: eight 16-byte pieces of this batch row, asynchronously
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(b_row + ((c ^ swz) << 4)),
-                             "l"(x_ptr + kb * kBK + c * 8)
-                             : "memory");
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            // weight tile: 64 codes of this row -> FP16 * scale, in memory order
-            const uint4 lo = ldg_stream16(w_ptr + kb * 32);
-            const uint4 hi = ldg_stream16(w_ptr + kb * 32 + 16);
-            const uint32_t s16 = ldg_nc_u16(s_ptr + (kb >> 1));
-            const uint32_t scale2 = s16 | (s16 << 16);
-            const uint32_t words[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t h[4];
-                unpack8(words[c], h);                       // (c0,c4) (c1,c5) (c2,c6) (c3,c7)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) h[j] = hmul2_u32(h[j], scale2);
-                const uint32_t v0 = prmt(h[0], h[1], 0x5410u);   // (c0,c1)
-                const uint32_t v1 = prmt(h[2], h[3], 0x5410u);   // (c2,c3)
-                const uint32_t v2 = prmt(h[0], h[1], 0x7632u);   // (c4,c5)
-                const uint32_t v3 = prmt(h[2], h[3], 0x7632u);   // (c6,c7)
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_row + ((c ^ swz) << 4)), "r"(v0), "r"(v1),
-                             "r"(v2), "r"(v3)
-                             : "memory");
-            }
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
-            mbar_arrive(full_bar(stage));
-        }
-    } else if (lane == 0) {
-        // ---------------- one thread issues the MMAs ------------------------------------------------
-        for (int kb = 0; kb < k_blocks && healthy; ++kb) {
-            const int stage = kb % kStagesTc;
-            const unsigned round = kb / kStagesTc;
-            healthy = mbar_wait(full_bar(stage), round & 1, 0x20u + stage);
-            if (!healthy) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint64_t a_desc = operand_desc(a_tiles + stage * kTileBytes);
-            const uint64_t b_desc = operand_desc(b_tiles + stage * kTileBytes);
-#pragma unroll
-            for (int j = 0; j < kBK / 16; ++j) {
-                // 16 k = 32 bytes further along the swizzled row: +2 in 16-byte address units
-                umma_f16(tmem_base, a_desc + 2 * j, b_desc + 2 * j, (kb > 0 || j > 0) ? 1u : 0u);
-            }
-            umma_commit(empty_bar(stage));   // arrives when these MMAs have finished reading the stage
-        }
-        umma_commit(done_bar);               // arrives when every MMA above has completed
-    }
-
-    // ---------------- epilogue: warps 0-3 read their 32 TMEM lanes (= 32 output channels) ---------------
-    if (warp < 4) {
-        const bool ready = mbar_wait(done_bar, 0, 0x30u);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const int n = n0 + warp * 32 + lane;
-        if (ready) {
-            for (int col = 0; col < kBN; col += 8) {
-                uint32_t v[8];
-                const unsigned taddr = tmem_base + (static_cast<unsigned>(warp * 32) << 16) + col;
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                             : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
-                             : "r"(taddr));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n < p.N) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int m = m0 + col + j;
-                        if (m < p.M) p.y[static_cast<size_t>(m) * p.N + n] = __float2half_rn(__uint_as_float(v[j]));
-                    }
+    if (warp == 0) {
+        // ---------------- TMA: the x tile of every stage ------------------------------------------------
+        if (lane == 0) {
+            unsigned it = 0;
+            const unsigned tile_bytes = static_cast<unsigned>(p.bn) * (kBK * 2);
+            for (int tile = blockIdx.x; tile < p.total_tiles && healthy; tile += gridDim.x) {
+                int m_tile, n_tile;
+                tile_coords(tile, p, m_tile, n_tile);
+                const int m0 = m_tile * p.bn;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int stage = it % kStagesTc;
+                    const unsigned round = it / kStagesTc;
+                    if (round > 0) healthy = mbar_wait(empty_bar(stage), (round - 1) & 1, 0x10u + stage);
+                    if (!healthy) break;
+                    mbar_arrive_expect_tx(full_bar(stage), tile_bytes);
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                        "[%0], [%1, {%2, %3}], [%4];"
+                        ::"r"(b_tile(stage)), "l"(reinterpret_cast<uint64_t>(&x_map)), "r"(kb * kBK), "r"(m0),
+                        "r"(full_bar(stage))
+                        : "memory");
                 }
             }
         }
+    } else if (warp == 1) {
+        // ---------------- one thread issues the MMAs ----------------------------------------------------
+        if (lane == 0) {
+            const uint32_t instr_desc = (1u << 4)                                        // FP32 accumulate
+                                        | (static_cast<uint32_t>(p.bn >> 3) << 17)       // N
+                                        | (static_cast<uint32_t>(kBM >> 4) << 24);       // M; FP16, K-major A and B
+            unsigned it = 0, done_tiles = 0;
+            for (int tile = blockIdx.x; tile < p.total_tiles && healthy; tile += gridDim.x, ++done_tiles) {
+                const unsigned buf = done_tiles & 1, use = done_tiles >> 1;
+                if (use > 0) healthy = mbar_wait(acc_empty_bar(buf), (use - 1) & 1, 0x40u + buf);
+                if (!healthy) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned acc = tmem_base + buf * kMaxBN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int stage = it % kStagesTc;
+                    const unsigned round = it / kStagesTc;
+                    healthy = mbar_wait(full_bar(stage), round & 1, 0x20u + stage);
+                    if (!healthy) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t a_desc = operand_desc(a_tile(stage));
+                    const uint64_t b_desc = operand_desc(b_tile(stage));
+#pragma unroll
+                    for (int j = 0; j < kBK / 16; ++j) {
+                        // 16 k = 32 bytes further along the swizzled row: +2 in 16-byte address units
+                        umma_f16(acc, a_desc + 2 * j, b_desc + 2 * j, instr_desc, (kb > 0 || j > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty_bar(stage));   // arrives when these MMAs have finished reading the stage
+                }
+                if (!healthy) break;
+                umma_commit(acc_full_bar(buf));      // arrives when the whole tile has been accumulated
+            }
+        }
+    } else if (warp < kFirstDequantWarp) {
+        // ---------------- epilogue: each warp owns the 32 TMEM lanes (output channels) it may address ----
+        const int quarter = warp & 3;
+        unsigned done_tiles = 0;
+        for (int tile = blockIdx.x; tile < p.total_tiles && healthy; tile += gridDim.x, ++done_tiles) {
+            int m_tile, n_tile;
+            tile_coords(tile, p, m_tile, n_tile);
+            const int m0 = m_tile * p.bn;
+            const int n = n_tile * kBM + quarter * 32 + lane;
+            const unsigned buf = done_tiles & 1, use = done_tiles >> 1;
+            healthy = mbar_wait(acc_full_bar(buf), use & 1, 0x30u + buf);
+            if (!healthy) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const unsigned taddr = tmem_base + (static_cast<unsigned>(quarter * 32) << 16) + buf * kMaxBN;
+            __half* out = p.y + static_cast<size_t>(m0) * p.N + n;
+            for (int col = 0; col < p.bn; col += 16) {
+                uint32_t v[16];
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                    : "r"(taddr + col));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (m0 + col + j < p.M) out[static_cast<size_t>(col + j) * p.N] = __float2half_rn(__uint_as_float(v[j]));
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(acc_empty_bar(buf));         // this thread's part of the accumulator is in registers or stored
+        }
+    } else {
+        // ---------------- dequantisers: threads 2r, 2r+1 share weight row r of the tile ------------------
+        const int t = tid - kFirstDequantWarp * 32;
+        const int r = t >> 1;
+        const int half_k = t & 1;                                        // which 32 of the 64 k of a block
+        const unsigned row_offset = (r >> 3) * 1024 + (r & 7) * 128;     // row r inside a swizzled tile
+        const unsigned swz = r & 7;
+        unsigned it = 0;
+        for (int tile = blockIdx.x; tile < p.total_tiles && healthy; tile += gridDim.x) {
+            int m_tile, n_tile;
+            tile_coords(tile, p, m_tile, n_tile);
+            const int w_row = min(n_tile * kBM + r, p.N - 1);
+            const uint8_t* w_ptr = p.packed + static_cast<size_t>(w_row) * (p.K >> 1) + half_k * 16;
+            const __half* s_ptr = p.scales + static_cast<size_t>(w_row) * (p.K / kGroup);
+            uint4 codes = ldg_stream16(w_ptr);
+            uint32_t s16 = ldg_nc_u16(s_ptr);
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int stage = it % kStagesTc;
+                const unsigned round = it / kStagesTc;
+                // next block's codes and scale are requested before this block's slot is waited for
+                const int kn = min(kb + 1, k_blocks - 1);
+                const uint4 next_codes = ldg_stream16(w_ptr + kn * 32);
+                const uint32_t next_s16 = ldg_nc_u16(s_ptr + (kn >> 1));
+                if (round > 0) healthy = mbar_wait(empty_bar(stage), (round - 1) & 1, 0x50u + stage);
+                if (!healthy) break;
+                const unsigned a_row = a_tile(stage) + row_offset;
+                const uint32_t scale2 = s16 | (s16 << 16);
+                const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t h[4];
+                    unpack8(words[c], h);                       // (c0,c4) (c1,c5) (c2,c6) (c3,c7)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) h[j] = hmul2_u32(h[j], scale2);
+                    const uint32_t v0 = prmt(h[0], h[1], 0x5410u);   // (c0,c1)
+                    const uint32_t v1 = prmt(h[2], h[3], 0x5410u);   // (c2,c3)
+                    const uint32_t v2 = prmt(h[0], h[1], 0x7632u);   // (c4,c5)
+                    const uint32_t v3 = prmt(h[2], h[3], 0x7632u);   // (c6,c7)
+                    const unsigned piece = static_cast<unsigned>(half_k * 4 + c) ^ swz;
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_row + (piece << 4)), "r"(v0), "r"(v1),
+                                 "r"(v2), "r"(v3)
+                                 : "memory");
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
+                mbar_arrive(full_bar(stage));
+                codes = next_codes;
+                s16 = next_s16;
+            }
+        }
     }
+
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 4) {
+    if (warp == 1) {
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kBN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns) : "memory");
     }
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up through the runtime so that libcuda is not a link dependency.
+EncodeTiledFn tensor_map_encoder() {
+    static EncodeTiledFn fn = [] {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult found;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &found) != cudaSuccess ||
+            found != cudaDriverEntryPointSuccess) {
+            entry = nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(entry);
+    }();
+    return fn;
 }
 
 }  // namespace
@@ -246,24 +345,46 @@ linear_tcgen05_kernel(const TcParams p) {
 int launch_linear_tcgen05(const LinearProblem& prob, cudaStream_t stream) {
     if (prob.group != kGroup || prob.K % kGroup != 0 || prob.K <= 0) return W4A16_ERR_BAD_CONFIG;
     if (prob.M > INT32_MAX || prob.N > INT32_MAX || prob.K > INT32_MAX) return W4A16_ERR_TOO_LARGE;
-    const int64_t grid_n = (prob.N + kBM - 1) / kBM;
-    const int64_t grid_m = (prob.M + kBN - 1) / kBN;
-    if (grid_m > 65535) return W4A16_ERR_TOO_LARGE;
-    TcParams params{prob.x, prob.packed, prob.scales, static_cast<__half*>(prob.y), static_cast<int>(prob.M),
-                    static_cast<int>(prob.N), static_cast<int>(prob.K)};
-    const size_t smem = 2 * kStagesTc * kTileBytes + 1024 /* alignment slack */ + 256 /* barriers, TMEM slot */;
-    // the attribute is kept per device
-    static bool configured[64] = {};
+    if (reinterpret_cast<uintptr_t>(prob.x) % 16 != 0) return W4A16_ERR_MISALIGNED;
+    const int64_t m_tiles = (prob.M + kMaxBN - 1) / kMaxBN;
+    const int64_t bn = (((prob.M + m_tiles - 1) / m_tiles) + 15) / 16 * 16;     // even split, multiple of 16, <= 256
+    const int64_t n_tiles = (prob.N + kBM - 1) / kBM;
+    if (m_tiles * n_tiles > INT32_MAX) return W4A16_ERR_TOO_LARGE;
+
+    const EncodeTiledFn encode = tensor_map_encoder();
+    if (encode == nullptr) return W4A16_ERR_LAUNCH;
+    CUtensorMap x_map;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(prob.K), static_cast<cuuint64_t>(prob.M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(prob.K) * 2};
+    const cuuint32_t box[2] = {kBK, static_cast<cuuint32_t>(bn)};
+    const cuuint32_t element_strides[2] = {1, 1};
+    // rows past M read as zero; the swizzle matches the MMA operand descriptor
+    if (encode(&x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(prob.x), dims, strides, box,
+               element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+        return W4A16_ERR_LAUNCH;
+    }
+
+    TcParams params{prob.packed, prob.scales, static_cast<__half*>(prob.y),
+                    static_cast<int>(prob.M), static_cast<int>(prob.N), static_cast<int>(prob.K),
+                    static_cast<int>(bn), static_cast<int>(m_tiles), static_cast<int>(n_tiles),
+                    static_cast<int>(m_tiles * n_tiles)};
+    const size_t smem = kStagesTc * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers, TMEM slot */;
+    // the shared-memory attribute and the SM count are kept per device
+    static int sm_count[64] = {};
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return W4A16_ERR_LAUNCH;
-    if (!configured[device]) {
+    if (sm_count[device] == 0) {
+        int sms = 0;
         if (cudaFuncSetAttribute(linear_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem)) != cudaSuccess) {
+                                 static_cast<int>(smem)) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
             return W4A16_ERR_LAUNCH;
         }
-        configured[device] = true;
+        sm_count[device] = sms;
     }
-    linear_tcgen05_kernel<<<dim3(static_cast<unsigned>(grid_n), static_cast<unsigned>(grid_m)), kThreadsTc, smem, stream>>>(params);
+    const int grid = static_cast<int>(std::min<int64_t>(params.total_tiles, sm_count[device]));
+    linear_tcgen05_kernel<<<grid, kThreadsTc, smem, stream>>>(params, x_map);
     if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return W4A16_OK;

@@ -50,6 +50,25 @@ def test_tcgen05_path_matches_oracle(m, k, n):
     torch.testing.assert_close(y, other, rtol=1e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize(("m", "k", "n"), [
+    (600, 512, 8192),      # 3 x 64 tiles: more tiles than SMs, every CTA reuses an accumulator buffer
+    (1024, 256, 16384),    # 512 tiles: at least three per CTA, both accumulator buffers recycled
+    (257, 1024, 1000),     # two ragged batch tiles, ragged last weight slab
+    (2048, 2048, 640),     # 8 batch tiles walked in groups
+])
+def test_tcgen05_many_tiles(m, k, n):
+    _device_status()
+    x, packed, scales = _case(m, k, n, seed=m ^ n)
+    y = capi_linear(x, packed, scales)
+    torch.cuda.synchronize()
+    assert _device_status() == 0
+    w16 = torch.from_numpy(oracle.dequantize_weights(packed.cpu().numpy(), scales.cpu().numpy(), 128).astype(np.float16))
+    ref = (x.float() @ w16.cuda().float().t())
+    torch.testing.assert_close(y.float(), ref, rtol=2e-3, atol=2e-3)
+    rows = np.random.default_rng(m).choice(n, size=64, replace=False)
+    check_against_oracle(y, x, packed, scales, rows=np.sort(rows), fp16_weights=True)
+
+
 def test_all_nibble_values_and_repeatability(golden):
     data = golden("all_nibbles.npz")
     packed = torch.from_numpy(data["packed"]).cuda()
