@@ -14,11 +14,13 @@
 // 256 batch rows.
 //
 // Persistent CTAs, one per SM, each walking a strided list of output tiles; 14 warps with fixed roles:
-//   warp 0      one lane issues the TMA loads of the x tile (tensor map built per call on the host)
+//   warp 0      one lane issues the TMA loads of every stage: the x tile and the packed codes of the
+//               weight tile (two tensor maps built per call on the host)
 //   warp 1      allocates TMEM; one lane issues the MMAs and the commits that recycle pipeline stages
 //   warps 2-5   epilogue: tcgen05.ld the accumulator of the finished tile, round to FP16, store
-//   warps 6-13  dequantisers: two threads per weight row, 32 codes each per 64-wide K block ->
-//               unpack, scale, re-pair to memory order, four 16-byte stores at their swizzled places
+//   warps 6-13  dequantisers: two threads per weight row, 32 codes each per 64-wide K block, read from
+//               the stage's packed tile -> unpack, scale, re-pair to memory order, four 16-byte stores
+//               at their swizzled places in the stage's FP16 operand tile
 // The accumulator is double buffered (2 x 256 TMEM columns), so the epilogue of one tile runs under
 // the main loop of the next.
 //
@@ -44,7 +46,8 @@ constexpr int kBK = 64;           // K per pipeline stage: one 128-byte swizzle 
 constexpr int kStagesTc = 4;
 constexpr int kATileBytes = kBM * kBK * 2;        // 16 KB
 constexpr int kBTileBytes = kMaxBN * kBK * 2;     // 32 KB
-constexpr int kStageBytes = kATileBytes + kBTileBytes;
+constexpr int kPackedTileBytes = kBM * kBK / 2;   // 4 KB: the codes of one weight tile as they lie in HBM
+constexpr int kStageBytes = kATileBytes + kBTileBytes + kPackedTileBytes;
 constexpr int kDequantThreads = 256;
 constexpr int kEpilogueThreads = 128;
 constexpr int kFirstDequantWarp = 6;
@@ -132,18 +135,21 @@ __device__ __forceinline__ void tile_coords(int tile, const TcParams& p, int& m_
 }
 
 __global__ void __launch_bounds__(kThreadsTc, 1)
-linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map) {
+linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
+                      const __grid_constant__ CUtensorMap w_map) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte aligned tiles (the swizzle pattern is a function of address bits 4-9)
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     auto a_tile = [&](int s) { return base + s * kStageBytes; };
     auto b_tile = [&](int s) { return base + s * kStageBytes + kATileBytes; };
+    auto packed_tile = [&](int s) { return base + s * kStageBytes + kATileBytes + kBTileBytes; };
     const unsigned bars = base + kStagesTc * kStageBytes;
-    auto full_bar = [&](int s) { return bars + s * 8; };
-    auto empty_bar = [&](int s) { return bars + (kStagesTc + s) * 8; };
-    auto acc_full_bar = [&](int b) { return bars + (2 * kStagesTc + b) * 8; };
-    auto acc_empty_bar = [&](int b) { return bars + (2 * kStagesTc + 2 + b) * 8; };
-    const unsigned tmem_slot = bars + (2 * kStagesTc + 4) * 8;
+    auto full_bar = [&](int s) { return bars + s * 8; };                       // operands of the stage are ready
+    auto empty_bar = [&](int s) { return bars + (kStagesTc + s) * 8; };        // the MMAs are done with the stage
+    auto codes_bar = [&](int s) { return bars + (2 * kStagesTc + s) * 8; };    // the packed codes have landed
+    auto acc_full_bar = [&](int b) { return bars + (3 * kStagesTc + b) * 8; };
+    auto acc_empty_bar = [&](int b) { return bars + (3 * kStagesTc + 2 + b) * 8; };
+    const unsigned tmem_slot = bars + (3 * kStagesTc + 4) * 8;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -154,6 +160,7 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
         for (int s = 0; s < kStagesTc; ++s) {
             mbar_init(full_bar(s), kDequantThreads + 1);   // every dequantiser thread + the TMA issuer
             mbar_init(empty_bar(s), 1);                    // one tcgen05.commit
+            mbar_init(codes_bar(s), 1);                    // the TMA issuer
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full_bar(b), 1);
@@ -161,6 +168,7 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&x_map)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&w_map)) : "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(kTmemColumns) : "memory");
@@ -174,7 +182,7 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
 
     bool healthy = true;
     if (warp == 0) {
-        // ---------------- TMA: the x tile of every stage ------------------------------------------------
+        // ---------------- TMA: the packed weight tile and the x tile of every stage ----------------------
         if (lane == 0) {
             unsigned it = 0;
             const unsigned tile_bytes = static_cast<unsigned>(p.bn) * (kBK * 2);
@@ -182,11 +190,19 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
                 int m_tile, n_tile;
                 tile_coords(tile, p, m_tile, n_tile);
                 const int m0 = m_tile * p.bn;
+                const int n0 = n_tile * kBM;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int stage = it % kStagesTc;
                     const unsigned round = it / kStagesTc;
                     if (round > 0) healthy = mbar_wait(empty_bar(stage), (round - 1) & 1, 0x10u + stage);
                     if (!healthy) break;
+                    mbar_arrive_expect_tx(codes_bar(stage), kPackedTileBytes);
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                        "[%0], [%1, {%2, %3}], [%4];"
+                        ::"r"(packed_tile(stage)), "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(kb * (kBK / 2)), "r"(n0),
+                        "r"(codes_bar(stage))
+                        : "memory");
                     mbar_arrive_expect_tx(full_bar(stage), tile_bytes);
                     asm volatile(
                         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
@@ -270,27 +286,35 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
         const int half_k = t & 1;                                        // which 32 of the 64 k of a block
         const unsigned row_offset = (r >> 3) * 1024 + (r & 7) * 128;     // row r inside a swizzled tile
         const unsigned swz = r & 7;
+        const unsigned codes_offset = r * (kBK / 2) + half_k * 16;       // this thread's 16 bytes of a packed tile
+        const int groups = p.K / kGroup;
         unsigned it = 0;
         for (int tile = blockIdx.x; tile < p.total_tiles && healthy; tile += gridDim.x) {
             int m_tile, n_tile;
             tile_coords(tile, p, m_tile, n_tile);
+            // rows past N hold zero codes (the tensor map fills them); their scale is the last row's
             const int w_row = min(n_tile * kBM + r, p.N - 1);
-            const uint8_t* w_ptr = p.packed + static_cast<size_t>(w_row) * (p.K >> 1) + half_k * 16;
-            const __half* s_ptr = p.scales + static_cast<size_t>(w_row) * (p.K / kGroup);
-            uint4 codes = ldg_stream16(w_ptr);
+            const __half* s_ptr = p.scales + static_cast<size_t>(w_row) * groups;
+            // a scale serves two K blocks and is requested two blocks before its first use
             uint32_t s16 = ldg_nc_u16(s_ptr);
+            uint32_t next_s16 = ldg_nc_u16(s_ptr + min(1, groups - 1));
             for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                 const int stage = it % kStagesTc;
                 const unsigned round = it / kStagesTc;
-                // next block's codes and scale are requested before this block's slot is waited for
-                const int kn = min(kb + 1, k_blocks - 1);
-                const uint4 next_codes = ldg_stream16(w_ptr + kn * 32);
-                const uint32_t next_s16 = ldg_nc_u16(s_ptr + (kn >> 1));
-                if (round > 0) healthy = mbar_wait(empty_bar(stage), (round - 1) & 1, 0x50u + stage);
+                if ((kb & 1) == 0 && kb > 0) {
+                    s16 = next_s16;
+                    next_s16 = ldg_nc_u16(s_ptr + min((kb >> 1) + 1, groups - 1));
+                }
+                // the codes landing also means the MMAs that last read this stage's operand tile are done:
+                // the issuer waited for that before it asked for the codes
+                healthy = mbar_wait(codes_bar(stage), round & 1, 0x50u + stage);
                 if (!healthy) break;
+                uint32_t words[4];
+                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3])
+                             : "r"(packed_tile(stage) + codes_offset));
                 const unsigned a_row = a_tile(stage) + row_offset;
                 const uint32_t scale2 = s16 | (s16 << 16);
-                const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t h[4];
@@ -308,8 +332,6 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
                 mbar_arrive(full_bar(stage));
-                codes = next_codes;
-                s16 = next_s16;
             }
         }
     }
@@ -345,7 +367,9 @@ EncodeTiledFn tensor_map_encoder() {
 int launch_linear_tcgen05(const LinearProblem& prob, cudaStream_t stream) {
     if (prob.group != kGroup || prob.K % kGroup != 0 || prob.K <= 0) return W4A16_ERR_BAD_CONFIG;
     if (prob.M > INT32_MAX || prob.N > INT32_MAX || prob.K > INT32_MAX) return W4A16_ERR_TOO_LARGE;
-    if (reinterpret_cast<uintptr_t>(prob.x) % 16 != 0) return W4A16_ERR_MISALIGNED;
+    if (reinterpret_cast<uintptr_t>(prob.x) % 16 != 0 || reinterpret_cast<uintptr_t>(prob.packed) % 16 != 0) {
+        return W4A16_ERR_MISALIGNED;
+    }
     const int64_t m_tiles = (prob.M + kMaxBN - 1) / kMaxBN;
     const int64_t bn = (((prob.M + m_tiles - 1) / m_tiles) + 15) / 16 * 16;     // even split, multiple of 16, <= 256
     const int64_t n_tiles = (prob.N + kBM - 1) / kBM;
@@ -362,6 +386,17 @@ int launch_linear_tcgen05(const LinearProblem& prob, cudaStream_t stream) {
     if (encode(&x_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half*>(prob.x), dims, strides, box,
                element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+        return W4A16_ERR_LAUNCH;
+    }
+
+    // packed codes as a byte matrix [N, K/2]; rows past N read as zero codes
+    CUtensorMap w_map;
+    const cuuint64_t w_dims[2] = {static_cast<cuuint64_t>(prob.K / 2), static_cast<cuuint64_t>(prob.N)};
+    const cuuint64_t w_strides[1] = {static_cast<cuuint64_t>(prob.K / 2)};
+    const cuuint32_t w_box[2] = {kBK / 2, kBM};
+    if (encode(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(prob.packed), w_dims, w_strides, w_box,
+               element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
         return W4A16_ERR_LAUNCH;
     }
 
@@ -384,7 +419,7 @@ int launch_linear_tcgen05(const LinearProblem& prob, cudaStream_t stream) {
         sm_count[device] = sms;
     }
     const int grid = static_cast<int>(std::min<int64_t>(params.total_tiles, sm_count[device]));
-    linear_tcgen05_kernel<<<grid, kThreadsTc, smem, stream>>>(params, x_map);
+    linear_tcgen05_kernel<<<grid, kThreadsTc, smem, stream>>>(params, x_map, w_map);
     if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return W4A16_OK;
