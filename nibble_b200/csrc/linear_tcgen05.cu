@@ -158,7 +158,7 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
 
     if (tid == 0) {
         for (int s = 0; s < kStagesTc; ++s) {
-            mbar_init(full_bar(s), kDequantThreads + 1);   // every dequantiser thread + the TMA issuer
+            mbar_init(full_bar(s), kDequantThreads / 32 + 1);   // one lane per dequantiser warp + the TMA issuer
             mbar_init(empty_bar(s), 1);                    // one tcgen05.commit
             mbar_init(codes_bar(s), 1);                    // the TMA issuer
         }
@@ -268,7 +268,12 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
                     : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
                       "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
                     : "r"(taddr + col));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                // the registers pass through the wait so that no use of them can be scheduled before it
+                asm volatile("tcgen05.wait::ld.sync.aligned;"
+                             : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]),
+                               "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                             :
+                             : "memory");
                 if (n < p.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -331,7 +336,8 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
                                  : "memory");
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
-                mbar_arrive(full_bar(stage));
+                __syncwarp();                                                  // every lane has written and fenced
+                if (lane == 0) mbar_arrive(full_bar(stage));
             }
         }
     }
