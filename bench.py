@@ -219,6 +219,53 @@ def per_shape_table(torch, shapes: dict, m: int, device, l2_bytes: int, with_cub
     return out
 
 
+def prefill_table(torch, device) -> dict:
+    """Prefill-sized batches: the tcgen05 kernel with fused dequantisation against the reference's route
+    (dequantise to FP16, then cuBLAS; w4a16/linear.py:132-152) and against cuBLAS alone on FP16 weights
+    that already exist.  Eager launches on one weight copy, median of 7 CUDA-event timings of 5 calls."""
+    from nibble_b200 import dequantize_cuda, linear_cuda
+
+    def timed(fn) -> float:
+        for _ in range(2):
+            fn()
+        samples = []
+        for _ in range(7):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(5):
+                fn()
+            end.record()
+            torch.cuda.synchronize()
+            samples.append(start.elapsed_time(end) * 1000.0 / 5)
+        return statistics.median(samples)
+
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    tensor_peak = json.loads(peaks_path.read_text()).get("bf16_tflops") if peaks_path.exists() else 1590.0
+    out = {}
+    shapes = {"tinyllama_gate_up": TINYLLAMA["gate_up_proj"], "llama70b_q_o": LLAMA70B["qo_proj"],
+              "llama70b_gate_up": LLAMA70B["gate_up_proj"]}
+    for index, (name, (k, n)) in enumerate(shapes.items()):
+        packed, scales = make_layer(torch, k, n, seed=50 + index, device=device)
+        w16 = dequantize_cuda(packed, scales, GROUP)
+        for m in (128, 512, 2048):
+            x = torch.randn((m, k), device=device).half()
+            fused = timed(lambda: linear_cuda(x, packed, scales, GROUP))
+            two_pass = timed(lambda: torch.nn.functional.linear(x, dequantize_cuda(packed, scales, GROUP)))
+            cublas = timed(lambda: torch.nn.functional.linear(x, w16))
+            exact = bool(torch.equal(linear_cuda(x, packed, scales, GROUP), torch.nn.functional.linear(x, w16)))
+            tflops = 2.0 * m * n * k / fused / 1e6
+            row = {"fused_us": round(fused, 1), "tflops": round(tflops, 1),
+                   "dequant_then_cublas_us": round(two_pass, 1), "speedup_vs_dequant_then_cublas": round(two_pass / fused, 2),
+                   "cublas_fp16_only_us": round(cublas, 1), "equals_cublas_on_fp16_weights": exact}
+            row["frac_of_bf16_peak"] = round(tflops / tensor_peak, 3)   # measured cuBLAS burst figure (fallback 1590)
+            out[f"{name}_m{m}"] = row
+            log(f"  prefill {name} K={k} N={n} M={m}: {row}")
+        del packed, scales, w16
+        torch.cuda.empty_cache()
+    return out
+
+
 def cpu_pass(torch, layers, sample_name: str, repeats: int) -> dict:
     """Times the CPU restatement on `layers` (list of (name, K, N)); returns GB/s over the sample."""
     from nibble_b200 import quantize_and_pack_weights
@@ -674,6 +721,8 @@ def run_product(args) -> dict:
             "llama70b_m1": per_shape_table(torch, LLAMA70B, 1, device, l2, with_cublas=False),
             "llama70b_m8": per_shape_table(torch, LLAMA70B, 8, device, l2, with_cublas=True),
         }
+        log("prefill-sized batches (tcgen05 kernel)")
+        result["prefill"] = prefill_table(torch, device)
     if rank == 0 and world == 1 and not args.quick:
         log("decode tokens/s, TinyLlama-1.1B-shaped model")
         try:

@@ -14,10 +14,26 @@ import torch.nn.functional as F
 from .cuda import dequantize_cuda, linear_cuda
 from .quantization import quantize_and_pack_weights
 
-# Largest flattened batch M sent to the fused kernel.  The reference stops at 8 and dequantises to
-# FP16 + cuBLAS above that (w4a16/linear.py:9,179-187); here the fused kernel keeps its advantage
-# (no FP16 matrix written and re-read) for prefill-sized batches as well.
+# Largest flattened batch M sent to the streaming (mma.sync) fused kernel.  The reference stops at 8
+# and dequantises to FP16 + cuBLAS above that (w4a16/linear.py:9,179-187).
 FUSED_MAX_ROWS = 64
+# Above FUSED_MAX_ROWS the operator runs the tcgen05 kernel that dequantises inside the GEMM.  It beats
+# dequantise-then-cuBLAS while the FP16 weight matrix's round trip through HBM is a large share of the
+# cuBLAS time (batches up to about a thousand rows) and there are enough 128-channel weight tiles to
+# occupy the GPU; outside that window the module does what the reference does.
+PREFILL_FUSED_MAX_ROWS = 1024
+PREFILL_MIN_WEIGHT_TILES = 40
+
+
+def uses_fused_kernel(rows: int, out_features: int, group_size: int) -> bool:
+    """Whether ``forward`` sends a flattened batch of ``rows`` to the fused operator."""
+    if rows <= FUSED_MAX_ROWS:
+        return True
+    if group_size % 32:
+        return True  # the dequantise operator needs group_size % 32 == 0; the fused one does not
+    if group_size != 128:
+        return False  # the tcgen05 kernel is built for 128-wide groups
+    return rows <= PREFILL_FUSED_MAX_ROWS and -(-out_features // 128) >= PREFILL_MIN_WEIGHT_TILES
 
 
 def _run_fused(flat, packed_weights, scales, group_size):
@@ -135,9 +151,8 @@ class QuantizedLinear(torch.nn.Module):
 
         # The operator wants a dense [M, K]; views handed over by generation loops often are not.
         flat = activations.contiguous().reshape(-1, self.in_features)
-        use_fused = self.fused and flat.shape[0] <= FUSED_MAX_ROWS
-        if not use_fused and self.group_size % 32:
-            use_fused = True  # the dequantise operator needs group_size % 32 == 0; the fused one does not
+        use_fused = (self.fused or self.group_size % 32 != 0) and uses_fused_kernel(
+            flat.shape[0], self.out_features, self.group_size)
         run = _run_fused if use_fused else _run_dequant_matmul
         flat_out = run(flat, self.packed_weights, self.scales, self.group_size)
         out = flat_out.reshape(*activations.shape[:-1], self.out_features)

@@ -70,7 +70,9 @@ def test_all_nibble_values(golden):
 @pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 6, 7, 8, 9, 15, 16, 17, 24, 32, 33, 70])
 def test_batch_sizes_on_2048_square(m):
     x, packed, scales = _random_case(m, 2048, 2048, seed=m)
-    check_against_oracle(capi_linear(x, packed, scales), x, packed, scales)
+    # from 65 rows on the tensor-core kernel runs: its weights are rounded to FP16 before the product,
+    # as in the reference's route for large batches
+    check_against_oracle(capi_linear(x, packed, scales), x, packed, scales, fp16_weights=m >= 65)
 
 
 @pytest.mark.parametrize("m", [1, 2, 8, 12])

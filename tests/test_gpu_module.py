@@ -58,6 +58,23 @@ def test_large_batch_and_unfused_mode_match_fp16_matmul_of_dequantised_weights()
     torch.testing.assert_close(layer(one), F.linear(one, w16), rtol=1e-3, atol=1e-3)
 
 
+def test_prefill_batch_on_a_wide_layer_takes_the_tensor_core_kernel():
+    from nibble_b200 import _native
+    from nibble_b200.linear import PREFILL_MIN_WEIGHT_TILES, uses_fused_kernel
+
+    n = 128 * PREFILL_MIN_WEIGHT_TILES
+    layer = _layer(n=n, k=1024, seed=3)
+    w16 = torch.from_numpy(
+        oracle.dequantize_weights(layer.packed_weights.cpu().numpy(), layer.scales.cpu().numpy(), 128).astype(np.float16)
+    ).cuda()
+    x = torch.randn((3, 100, 1024), dtype=torch.float16, device="cuda")
+    assert uses_fused_kernel(300, n, 128)
+    before = _native.core().w4a16_launch_count()
+    out = layer(x)
+    assert _native.core().w4a16_launch_count() == before + 1      # one fused launch, no dequantise pass
+    torch.testing.assert_close(out, F.linear(x, w16), rtol=2e-3, atol=2e-3)
+
+
 def test_replace_linear_layers_on_cuda_model():
     torch.manual_seed(1)
     model = torch.nn.Sequential(

@@ -79,6 +79,25 @@ def test_routing_by_rows_and_fused_flag(oracle_backend):
     assert oracle_backend == ["fused", "dequant", "dequant", "dequant"]
 
 
+def test_prefill_window_routes_wide_layers_to_the_fused_operator(oracle_backend):
+    from nibble_b200.linear import PREFILL_FUSED_MAX_ROWS, PREFILL_MIN_WEIGHT_TILES, uses_fused_kernel
+
+    wide = 128 * PREFILL_MIN_WEIGHT_TILES
+    assert uses_fused_kernel(FUSED_MAX_ROWS + 1, wide, 128)
+    assert uses_fused_kernel(PREFILL_FUSED_MAX_ROWS, wide, 128)
+    assert not uses_fused_kernel(PREFILL_FUSED_MAX_ROWS + 1, wide, 128)
+    assert not uses_fused_kernel(FUSED_MAX_ROWS + 1, wide - 128, 128)     # too few weight tiles to fill the GPU
+    assert not uses_fused_kernel(FUSED_MAX_ROWS + 1, wide, 64)            # tensor-core kernel is for 128-wide groups
+    assert uses_fused_kernel(10_000, 8, 4)                                # no dequantise operator for this group size
+    packed, scales = quantize_and_pack_weights(torch.randn(wide, 128).half(), 128)
+    layer = QuantizedLinear(packed, scales, 128)
+    layer(torch.zeros((FUSED_MAX_ROWS + 1, 128), dtype=torch.float16))
+    layer(torch.zeros((4, PREFILL_FUSED_MAX_ROWS // 4 + 1, 128), dtype=torch.float16))
+    layer.fused = False
+    layer(torch.zeros((FUSED_MAX_ROWS + 1, 128), dtype=torch.float16))
+    assert oracle_backend == ["fused", "dequant", "dequant"]
+
+
 def test_group_size_without_dequantize_kernel_stays_fused(oracle_backend):
     layer = _layer(fused=False)  # group_size 4 is not a multiple of 32
     layer(ACTIVATIONS)
