@@ -397,7 +397,15 @@ def decode_bench(torch, device) -> dict:
     out["w4a16"] = measure("w4a16")
     os.environ["W4A16_PDL"] = "1"
     out["w4a16_programmatic_launch"] = measure("w4a16+pdl")
+    from nibble_b200 import fuse_parallel_linears
+
+    out["launches_fused"] = fuse_parallel_linears(model)     # q/k/v -> one launch, gate/up -> one launch per block
+    torch.cuda.empty_cache()
+    # with every fused launch sitting between two torch kernels there is no chain of our own kernels left
+    # for programmatic launch to overlap, and the attribute costs time: measured both ways
+    out["w4a16_programmatic_launch_fused_qkv_gate_up"] = measure("w4a16+pdl+fused q/k/v, gate/up")
     os.environ.pop("W4A16_PDL", None)
+    out["w4a16_fused_qkv_gate_up"] = measure("w4a16+fused q/k/v, gate/up")
     if saved_pdl is not None:
         os.environ["W4A16_PDL"] = saved_pdl
     del model

@@ -160,6 +160,18 @@ int w4a16_dequantize_f16(const void* packed, const void* scales, void* weights,
                          int64_t N, int64_t K, int64_t group_size, w4a16_stream_t stream);
 
 /*
+ * FP16 / FP32 weights [N, K] -> packed codes [N, K/2] and FP16 scales [N, K/group_size] on the device,
+ * bit-identical to the reference's host quantiser quantize_and_pack_weights
+ * (w4a16/quantization.py:65-113): step = absmax/7 in FP32 (1 for an all-zero group),
+ * code = clamp(round_half_even(w / step), -7, 7), scale = half(step).  group_size: positive, even,
+ * dividing K.  The reference has no device version of this step.
+ */
+int w4a16_quantize_pack_f16(const void* weights, void* packed, void* scales,
+                            int64_t N, int64_t K, int64_t group_size, w4a16_stream_t stream);
+int w4a16_quantize_pack_f32(const void* weights, void* packed, void* scales,
+                            int64_t N, int64_t K, int64_t group_size, w4a16_stream_t stream);
+
+/*
  * w4a16_linear_f16 for callers that cannot allocate device memory (no cudaMalloc after start-up,
  * no workspace handed to a plugin, an open stream capture): the split-K scratch is a fixed array
  * inside the library's device image, w4a16_static_scratch_bytes() bytes per GPU, instead of a

@@ -1,6 +1,7 @@
 """B200-native W4A16 linear path with the reference project's Python surface."""
 from .checkpoint import load_quantized_weight_checkpoint, save_quantized_weight_checkpoint
-from .cuda import cuda_extension_available, dequantize_cuda, linear_cuda
+from .cuda import cuda_extension_available, dequantize_cuda, linear_cuda, quantize_and_pack_cuda
+from .fusion import FusedQuantizedLinear, FusedSlice, fuse_parallel_linears
 from .integration import load_packed_state_dict, replace_linear_layers
 from .linear import Int4Linear, QuantizedLinear
 from .quantization import pack_int4, quantize_and_pack_weights, quantize_groupwise, unpack_int4
@@ -16,7 +17,11 @@ __all__ = [
     "load_quantized_weight_checkpoint",
     "replace_linear_layers",
     "load_packed_state_dict",
+    "fuse_parallel_linears",
+    "FusedQuantizedLinear",
+    "FusedSlice",
     "linear_cuda",
     "dequantize_cuda",
+    "quantize_and_pack_cuda",
     "cuda_extension_available",
 ]

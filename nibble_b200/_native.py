@@ -65,6 +65,8 @@ C_API = {
     "w4a16_wait_peers": (ctypes.c_int, [_P, _P, ctypes.c_int32, _P, _I, _P]),
     "w4a16_sum_partials_f16": (ctypes.c_int, [_P, _P, _I, ctypes.c_int32, _P, _P, _P, _I, _P]),
     "w4a16_dequantize_f16": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
+    "w4a16_quantize_pack_f16": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
+    "w4a16_quantize_pack_f32": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
     "w4a16_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32)]),
     "w4a16_launch_count": (ctypes.c_uint64, []),
     "w4a16_status_string": (ctypes.c_char_p, [ctypes.c_int]),

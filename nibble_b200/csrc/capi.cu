@@ -185,4 +185,29 @@ int w4a16_dequantize_f16(const void* packed, const void* scales, void* weights, 
                                     reinterpret_cast<cudaStream_t>(stream));
 }
 
+static int quantize_pack(const void* weights, bool is_f32, void* packed, void* scales, int64_t N, int64_t K,
+                         int64_t group_size, w4a16_stream_t stream) {
+    if (N < 0 || K < 0 || (K & 1)) return W4A16_ERR_BAD_SHAPE;
+    if (group_size <= 0 || (group_size & 1) || group_size > INT32_MAX) return W4A16_ERR_BAD_GROUP;
+    if (K % group_size != 0) return W4A16_ERR_BAD_SHAPE;
+    if (N == 0 || K == 0) return W4A16_OK;
+    if (weights == nullptr || packed == nullptr || scales == nullptr) return W4A16_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(packed) % 2 != 0 || reinterpret_cast<uintptr_t>(scales) % 2 != 0 ||
+        reinterpret_cast<uintptr_t>(weights) % (is_f32 ? 4 : 2) != 0) {
+        return W4A16_ERR_MISALIGNED;
+    }
+    return w4a16::launch_quantize_pack(weights, is_f32, static_cast<uint8_t*>(packed), static_cast<__half*>(scales), N, K,
+                                       group_size, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int w4a16_quantize_pack_f16(const void* weights, void* packed, void* scales, int64_t N, int64_t K, int64_t group_size,
+                            w4a16_stream_t stream) {
+    return quantize_pack(weights, false, packed, scales, N, K, group_size, stream);
+}
+
+int w4a16_quantize_pack_f32(const void* weights, void* packed, void* scales, int64_t N, int64_t K, int64_t group_size,
+                            w4a16_stream_t stream) {
+    return quantize_pack(weights, true, packed, scales, N, K, group_size, stream);
+}
+
 }  // extern "C"

@@ -164,6 +164,29 @@ at::Tensor dequantize_cuda_impl(const at::Tensor& packed_weights, const at::Tens
     return weights;
 }
 
+std::tuple<at::Tensor, at::Tensor> quantize_pack_cuda_impl(const at::Tensor& weights, int64_t group_size) {
+    TORCH_CHECK(weights.is_cuda(), "weights must be a CUDA tensor");
+    TORCH_CHECK(weights.scalar_type() == at::kHalf || weights.scalar_type() == at::kFloat,
+                "weights must have dtype torch.float16 or torch.float32");
+    TORCH_CHECK(weights.dim() == 2, "weights must have shape [N, K]");
+    TORCH_CHECK(group_size > 0, "group_size must be greater than zero");
+    TORCH_CHECK(weights.size(1) % group_size == 0, "K must be divisible by group_size");
+    TORCH_CHECK(weights.size(1) % 2 == 0 && group_size % 2 == 0, "K and group_size must be even: one byte carries two weights");
+    const at::Tensor dense = weights.contiguous();
+    const int64_t n = dense.size(0);
+    const int64_t k = dense.size(1);
+    const c10::cuda::CUDAGuard guard(dense.device());
+    at::Tensor packed = at::empty({n, k / 2}, dense.options().dtype(at::kByte));
+    at::Tensor scales = at::empty({n, k / group_size}, dense.options().dtype(at::kHalf));
+    if (n == 0 || k == 0) return {packed, scales};
+    const auto stream = reinterpret_cast<w4a16_stream_t>(at::cuda::getCurrentCUDAStream().stream());
+    const int status = dense.scalar_type() == at::kFloat
+                           ? w4a16_quantize_pack_f32(dense.data_ptr(), packed.data_ptr(), scales.data_ptr(), n, k, group_size, stream)
+                           : w4a16_quantize_pack_f16(dense.data_ptr(), packed.data_ptr(), scales.data_ptr(), n, k, group_size, stream);
+    check_status(status, "w4a16::quantize_pack");
+    return {packed, scales};
+}
+
 }  // namespace
 
 TORCH_LIBRARY(w4a16, m) {
@@ -171,10 +194,13 @@ TORCH_LIBRARY(w4a16, m) {
     m.def("dequantize(Tensor packed_weights, Tensor scales, int group_size) -> Tensor");
     // not in the reference: FP32 partial sums for layers sharded along K
     m.def("linear_partial(Tensor activations, Tensor packed_weights, Tensor scales, int group_size) -> Tensor");
+    // not in the reference: its quantiser is host code (w4a16/quantization.py:65-113)
+    m.def("quantize_pack(Tensor weights, int group_size) -> (Tensor, Tensor)");
 }
 
 TORCH_LIBRARY_IMPL(w4a16, CUDA, m) {
     m.impl("linear", &linear_cuda_impl);
     m.impl("dequantize", &dequantize_cuda_impl);
     m.impl("linear_partial", &linear_partial_cuda_impl);
+    m.impl("quantize_pack", &quantize_pack_cuda_impl);
 }

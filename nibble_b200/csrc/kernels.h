@@ -61,4 +61,8 @@ int launch_sum_partials(const float* partials, __half* y, int64_t count, int wor
 int launch_dequantize(const uint8_t* packed, const __half* scales, __half* weights, int64_t N,
                       int64_t K, int64_t group, cudaStream_t stream);
 
+// Quantise + pack on the device (quantize.cu): FP16 or FP32 weights -> packed codes and FP16 scales.
+int launch_quantize_pack(const void* weights, bool is_f32, uint8_t* packed, __half* scales, int64_t N, int64_t K,
+                         int64_t group, cudaStream_t stream);
+
 }  // namespace w4a16

@@ -1,0 +1,87 @@
+// Group-wise symmetric INT4 quantisation and packing on the device: FP16 or FP32 weights [N, K] ->
+// packed codes [N, K/2] + FP16 scales [N, K/group], bit-identical to the reference's host routine
+// (w4a16/quantization.py:65-113):
+//   step  = amax(|w| over the group) / 7 in FP32, 1 for an all-zero group
+//   code  = clamp(round_half_even(w / step), -7, 7)        (FP32 IEEE division, rint)
+//   scale = half(step)                                     (rounded after the codes are made)
+// byte j of a row holds code 2j in its low nibble and code 2j+1 in its high nibble.
+//
+// One warp per group.  A lane takes four consecutive weights per pass (one 8- or 16-byte load, one
+// 2-byte store), so a 128-wide group is one pass; the group maximum is a shuffle reduction.  The
+// weights are read twice (maximum, then codes); the second read hits L1/L2.  Bound: HBM, 2.5 (FP16
+// input) or 4.5 (FP32) bytes per weight.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "kernels.h"
+
+namespace w4a16 {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float load_weight(const T* p);
+template <>
+__device__ __forceinline__ float load_weight<__half>(const __half* p) { return __half2float(*p); }
+template <>
+__device__ __forceinline__ float load_weight<float>(const float* p) { return *p; }
+
+__device__ __forceinline__ unsigned code_of(float w, float step) {
+    float q = rintf(__fdiv_rn(w, step));
+    q = fminf(fmaxf(q, -7.0f), 7.0f);
+    return static_cast<unsigned>(static_cast<int>(q)) & 0xFu;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_pack_kernel(const T* __restrict__ weights, uint8_t* __restrict__ packed, __half* __restrict__ scales,
+                     int64_t total_groups, int group) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 5);
+    for (int64_t g = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); g < total_groups; g += warps) {
+        const T* src = weights + g * group;              // groups of a row-major matrix are consecutive in memory
+        float amax = 0.0f;
+        for (int i = lane; i < group; i += 32) amax = fmaxf(amax, fabsf(load_weight(src + i)));
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+        const float step = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 7.0f);
+        uint8_t* dst = packed + g * (group >> 1);
+        if ((group & 3) == 0) {
+            for (int q = lane; q < (group >> 2); q += 32) {
+                const unsigned c0 = code_of(load_weight(src + 4 * q), step);
+                const unsigned c1 = code_of(load_weight(src + 4 * q + 1), step);
+                const unsigned c2 = code_of(load_weight(src + 4 * q + 2), step);
+                const unsigned c3 = code_of(load_weight(src + 4 * q + 3), step);
+                // (g * group / 2 + 2 q) is even: the two bytes are 2-byte aligned when `packed` is
+                *reinterpret_cast<uint16_t*>(dst + 2 * q) = static_cast<uint16_t>(c0 | (c1 << 4) | (c2 << 8) | (c3 << 12));
+            }
+        } else {
+            for (int q = lane; q < (group >> 1); q += 32) {
+                const unsigned c0 = code_of(load_weight(src + 2 * q), step);
+                const unsigned c1 = code_of(load_weight(src + 2 * q + 1), step);
+                dst[q] = static_cast<uint8_t>(c0 | (c1 << 4));
+            }
+        }
+        if (lane == 0) scales[g] = __float2half_rn(step);
+    }
+}
+
+template <typename T>
+int launch(const T* weights, uint8_t* packed, __half* scales, int64_t N, int64_t K, int64_t group, cudaStream_t stream) {
+    const int64_t total_groups = N * (K / group);
+    const int64_t blocks = std::min<int64_t>((total_groups + 7) / 8, 148 * 64);
+    quantize_pack_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(weights, packed, scales, total_groups,
+                                                                              static_cast<int>(group));
+    if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    return W4A16_OK;
+}
+
+}  // namespace
+
+int launch_quantize_pack(const void* weights, bool is_f32, uint8_t* packed, __half* scales, int64_t N, int64_t K,
+                         int64_t group, cudaStream_t stream) {
+    if (is_f32) return launch(static_cast<const float*>(weights), packed, scales, N, K, group, stream);
+    return launch(static_cast<const __half*>(weights), packed, scales, N, K, group, stream);
+}
+
+}  // namespace w4a16

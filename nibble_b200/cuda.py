@@ -30,6 +30,12 @@ def _register_fakes() -> None:
             (packed_weights.shape[0], packed_weights.shape[1] * 2), dtype=torch.float16
         )
 
+    @torch.library.register_fake("w4a16::quantize_pack")
+    def _quantize_pack_fake(weights, group_size):
+        rows, cols = weights.shape
+        return (weights.new_empty((rows, cols // 2), dtype=torch.uint8),
+                weights.new_empty((rows, cols // group_size), dtype=torch.float16))
+
 
 try:
     _native.load_torch_ops()
@@ -116,3 +122,11 @@ def linear_partial_cuda(
     """
     _require_extension()
     return torch.ops.w4a16.linear_partial(activations, packed_weights, scales, group_size)
+
+
+def quantize_and_pack_cuda(weights: torch.Tensor, group_size: int = 128) -> tuple[torch.Tensor, torch.Tensor]:
+    """FP16/FP32 CUDA weights ``[N, K]`` -> (packed uint8 ``[N, K/2]``, FP16 scales ``[N, K/group_size]``)
+    in one kernel, bit-identical to ``quantize_and_pack_weights`` (the reference's host routine,
+    w4a16/quantization.py:65-113).  Not part of the reference's surface."""
+    _require_extension()
+    return torch.ops.w4a16.quantize_pack(weights, group_size)

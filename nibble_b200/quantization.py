@@ -82,6 +82,16 @@ def quantize_and_pack_weights(
     weights: torch.Tensor,
     group_size: int = 128,
 ) -> tuple[torch.Tensor, torch.Tensor]:
-    """``quantize_groupwise`` then ``pack_int4``: (uint8 ``[N, K/2]``, FP16 ``[N, K/group_size]``)."""
+    """``quantize_groupwise`` then ``pack_int4``: (uint8 ``[N, K/2]``, FP16 ``[N, K/group_size]``).
+
+    CUDA weights with an even ``group_size`` go through the one-pass device kernel (same bits) when the
+    extension is built; everything else runs the torch operators below on the tensor's device.
+    """
+    if weights.is_cuda and weights.ndim == 2 and weights.dtype in (torch.float16, torch.float32) \
+            and group_size > 0 and group_size % 2 == 0 and weights.shape[1] % group_size == 0:
+        from . import cuda as _cuda   # late: this module must import without the extension
+
+        if _cuda.cuda_extension_available():
+            return _cuda.quantize_and_pack_cuda(weights, group_size)
     codes, scales = quantize_groupwise(weights, group_size)
     return pack_int4(codes), scales

@@ -118,3 +118,33 @@ def test_traces_under_torch_compile_aot_eager(rows):
     x = torch.randn((rows, 256), dtype=torch.float16, device="cuda")
     compiled = torch.compile(layer, backend="aot_eager", fullgraph=True)
     assert torch.equal(compiled(x), layer(x))
+
+
+def test_fused_siblings_one_launch_same_numbers():
+    from nibble_b200 import _native, fuse_parallel_linears
+
+    class Attn(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj = torch.nn.Linear(2048, 2048, bias=False)
+            self.k_proj = torch.nn.Linear(2048, 256, bias=False)
+            self.v_proj = torch.nn.Linear(2048, 256, bias=False)
+
+        def forward(self, x):
+            return self.q_proj(x), self.k_proj(x), self.v_proj(x)
+
+    torch.manual_seed(4)
+    attn = Attn().half().cuda()
+    assert replace_linear_layers(attn, group_size=128) == 3
+    x = torch.randn((1, 1, 2048), dtype=torch.float16, device="cuda")
+    separate = [t.clone() for t in attn(x)]
+    packed = [m.packed_weights.clone() for m in (attn.q_proj, attn.k_proj, attn.v_proj)]
+    scales = [m.scales.clone() for m in (attn.q_proj, attn.k_proj, attn.v_proj)]
+    assert fuse_parallel_linears(attn) == 1
+    before = _native.core().w4a16_launch_count()
+    fused = attn(x)
+    assert _native.core().w4a16_launch_count() == before + 1
+    for got, ref, p, s in zip(fused, separate, packed, scales):
+        assert got.shape == ref.shape
+        torch.testing.assert_close(got, ref, rtol=1e-2, atol=1e-2)
+        check_against_oracle(got.reshape(1, -1), x.reshape(1, -1), p, s)
