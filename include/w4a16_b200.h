@@ -172,6 +172,29 @@ int w4a16_quantize_pack_f32(const void* weights, void* packed, void* scales,
                             int64_t N, int64_t K, int64_t group_size, w4a16_stream_t stream);
 
 /*
+ * The three kernels either side of the linears in one LLaMA decode step (batch 1), for a runner
+ * that replaces the framework's decoder-layer code (the reference drives HuggingFace's
+ * model.generate, scripts/generate.py:260-365; the arithmetic restated is transformers'
+ * LlamaRMSNorm, apply_rotary_pos_emb, grouped-KV scaled-dot-product attention and LlamaMLP).
+ *
+ * add_rmsnorm: s = half(stream_in + delta) (delta may be NULL); stream_out = s (may be NULL or alias
+ *   stream_in); normed = weight * half(float(s) * rsqrt(mean(float(s)^2) + eps)).  One row of `hidden`.
+ * silu_mul: out[i] = half(silu(gate_up[i])) * gate_up[intermediate + i].
+ * attention_decode: qkv = [q_heads*d | kv_heads*d | kv_heads*d] of the token at *position (device
+ *   scalar); applies RoPE (cos, sin of position * inv_freq[j], times rope_scale, rounded to FP16) to
+ *   q and k, writes k and v into caches laid out [kv_heads][max_len][d], and writes
+ *   softmax(q k^T * softmax_scale) v over positions 0..*position to out [q_heads*d].  d is 64 or
+ *   128.  A position outside [0, max_len) sets *status to 1 and nothing is written.
+ */
+int w4a16_add_rmsnorm_f16(const void* stream_in, const void* delta, const void* weight, void* stream_out,
+                          void* normed, int64_t hidden, float eps, w4a16_stream_t stream);
+int w4a16_silu_mul_f16(const void* gate_up, void* out, int64_t intermediate, w4a16_stream_t stream);
+int w4a16_attention_decode_f16(const void* qkv, void* k_cache, void* v_cache, void* out,
+                               const int64_t* position, const float* inv_freq, int32_t q_heads,
+                               int32_t kv_heads, int32_t head_dim, int32_t max_len, float rope_scale,
+                               float softmax_scale, uint32_t* status, w4a16_stream_t stream);
+
+/*
  * w4a16_linear_f16 for callers that cannot allocate device memory (no cudaMalloc after start-up,
  * no workspace handed to a plugin, an open stream capture): the split-K scratch is a fixed array
  * inside the library's device image, w4a16_static_scratch_bytes() bytes per GPU, instead of a

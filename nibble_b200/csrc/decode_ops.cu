@@ -1,0 +1,231 @@
+// The small kernels either side of the linear layers in one LLaMA decode step (batch 1), so that a
+// token is ~8 launches per decoder block instead of the several dozen elementwise kernels a
+// framework issues:
+//   add_rmsnorm   residual add (FP16) + RMSNorm with FP32 statistics          -> input of q/k/v or gate/up
+//   attention     RoPE on q and k, append k/v to the cache, softmax(q k^T / sqrt(d)) v over the cache
+//   silu_mul      silu(gate) * up on the fused gate/up output                   -> input of down_proj
+// They restate what the reference's generation script gets from HuggingFace's LlamaDecoderLayer
+// (scripts/generate.py:260-365 drives model.generate; the arithmetic is transformers' modeling_llama:
+// LlamaRMSNorm, apply_rotary_pos_emb / rotate_half, scaled dot product attention with grouped KV heads,
+// LlamaMLP).  Roundings follow that code: the residual sum, the normalised value, the rotary
+// products and silu(gate) are each rounded to FP16 where the framework rounds them.
+//
+// The position is read from device memory, so one captured graph serves every step.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "kernels.h"
+
+namespace w4a16 {
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    __syncthreads();                       // scratch may still be read from a previous call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.0f;
+    for (int w = 0; w < warps; ++w) total += scratch[w];
+    return total;
+}
+
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float best = scratch[0];
+    for (int w = 1; w < warps; ++w) best = fmaxf(best, scratch[w]);
+    return best;
+}
+
+// stream_out = half(stream_in + delta) (or stream_in when delta is null); normed = weight * half(s * rsqrt(mean(s^2) + eps))
+__global__ void __launch_bounds__(256)
+add_rmsnorm_kernel(const __half* __restrict__ stream_in, const __half* __restrict__ delta, const __half* __restrict__ weight,
+                   __half* __restrict__ stream_out, __half* __restrict__ normed, int hidden, float eps) {
+    __shared__ float scratch[8];
+    extern __shared__ __half row[];        // the summed stream, kept for the second pass
+    float sq = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        __half s = stream_in[i];
+        if (delta != nullptr) s = __hadd(s, delta[i]);
+        row[i] = s;
+        const float f = __half2float(s);
+        sq += f * f;
+    }
+    const float inv = rsqrtf(block_sum(sq, scratch) / static_cast<float>(hidden) + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const __half s = row[i];
+        if (stream_out != nullptr) stream_out[i] = s;
+        normed[i] = __hmul(weight[i], __float2half_rn(__half2float(s) * inv));
+    }
+}
+
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ out, int inter) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= inter) return;
+    const float g = __half2float(gate_up[i]);
+    const __half act = __float2half_rn(g / (1.0f + expf(-g)));
+    out[i] = __hmul(act, gate_up[inter + i]);
+}
+
+struct AttentionParams {
+    const __half* qkv;        // [q heads * d | kv heads * d | kv heads * d] of this token
+    __half* k_cache;          // [kv heads][max_len][d]
+    __half* v_cache;
+    __half* out;              // [q heads * d]
+    const long long* position;  // device scalar: index of this token
+    const float* inv_freq;    // [d / 2]
+    int q_heads, kv_heads, head_dim, max_len;
+    float rope_scale;         // multiplies cos and sin (1 for plain RoPE)
+    float softmax_scale;
+    unsigned* status;         // set to 1 when the position does not fit the cache
+};
+
+// One CTA per query head, 128 threads, head_dim 64 or 128.
+__global__ void __launch_bounds__(128)
+attention_decode_kernel(const AttentionParams p) {
+    extern __shared__ float scores[];                 // max_len floats, then q (head_dim floats), then partial sums
+    __shared__ float scratch[4];
+    const int head = blockIdx.x;
+    const int d = p.head_dim;
+    const int half_d = d >> 1;
+    const int kv_head = head / (p.q_heads / p.kv_heads);
+    const long long pos = *p.position;
+    if (pos < 0 || pos >= p.max_len) {
+        if (threadIdx.x == 0) atomicMax(p.status, 1u);
+        return;
+    }
+    float* q = scores + p.max_len;
+    float* partial = q + d;                           // [4][d]
+    __shared__ __half k_new[128], v_new[128];
+
+    const __half* q_in = p.qkv + head * d;
+    const __half* k_in = p.qkv + p.q_heads * d + kv_head * d;
+    const __half* v_in = p.qkv + (p.q_heads + p.kv_heads) * d + kv_head * d;
+    // rotary embedding, rounded as the framework rounds it: cos/sin to FP16, two FP16 products, one FP16 sum
+    if (threadIdx.x < d) {
+        const int i = threadIdx.x;
+        const int f = i < half_d ? i : i - half_d;
+        const float angle = static_cast<float>(pos) * p.inv_freq[f];
+        const __half c = __float2half_rn(cosf(angle) * p.rope_scale);
+        const __half s = __float2half_rn(sinf(angle) * p.rope_scale);
+        const __half q_rot = i < half_d ? __hneg(q_in[i + half_d]) : q_in[i - half_d];
+        const __half k_rot = i < half_d ? __hneg(k_in[i + half_d]) : k_in[i - half_d];
+        // the _rn forms are never contracted into one fused multiply-add: two roundings, then a third
+        q[i] = __half2float(__hadd_rn(__hmul_rn(q_in[i], c), __hmul_rn(q_rot, s)));
+        const __half k_val = __hadd_rn(__hmul_rn(k_in[i], c), __hmul_rn(k_rot, s));
+        k_new[i] = k_val;
+        v_new[i] = v_in[i];
+        if (head % (p.q_heads / p.kv_heads) == 0) {   // one CTA per KV head appends to the cache
+            p.k_cache[(static_cast<size_t>(kv_head) * p.max_len + pos) * d + i] = k_val;
+            p.v_cache[(static_cast<size_t>(kv_head) * p.max_len + pos) * d + i] = v_in[i];
+        }
+    }
+    __syncthreads();
+
+    const int length = static_cast<int>(pos) + 1;
+    const __half* k_base = p.k_cache + static_cast<size_t>(kv_head) * p.max_len * d;
+    const __half* v_base = p.v_cache + static_cast<size_t>(kv_head) * p.max_len * d;
+    // scores: one thread per cached position (the newest comes from shared memory, not from the cache,
+    // because another CTA writes it)
+    float local_max = -INFINITY;
+    for (int t = threadIdx.x; t < length; t += blockDim.x) {
+        float dot = 0.0f;
+        if (t == length - 1) {
+            for (int i = 0; i < d; ++i) dot += q[i] * __half2float(k_new[i]);
+        } else {
+            const __half2* k_row = reinterpret_cast<const __half2*>(k_base + static_cast<size_t>(t) * d);
+            for (int i = 0; i < half_d; ++i) {
+                const float2 kk = __half22float2(k_row[i]);
+                dot += q[2 * i] * kk.x + q[2 * i + 1] * kk.y;
+            }
+        }
+        dot *= p.softmax_scale;
+        scores[t] = dot;
+        local_max = fmaxf(local_max, dot);
+    }
+    const float top = block_max(local_max, scratch);
+    float local_sum = 0.0f;
+    for (int t = threadIdx.x; t < length; t += blockDim.x) {
+        const float e = expf(scores[t] - top);
+        scores[t] = e;
+        local_sum += e;
+    }
+    const float denom = block_sum(local_sum, scratch);   // also makes every score visible
+    // values: thread = (quarter of the positions, pair of dims when d == 64; single dim pair loop otherwise)
+    const int pairs = half_d;                              // half2 columns
+    const int groups = blockDim.x / pairs > 0 ? blockDim.x / pairs : 1;
+    const int group = threadIdx.x / pairs;
+    const int pair = threadIdx.x % pairs;
+    float ax = 0.0f, ay = 0.0f;
+    if (group < groups) {
+        for (int t = group; t < length; t += groups) {
+            const float w = scores[t];
+            float2 vv;
+            if (t == length - 1) vv = make_float2(__half2float(v_new[2 * pair]), __half2float(v_new[2 * pair + 1]));
+            else vv = __half22float2(reinterpret_cast<const __half2*>(v_base + static_cast<size_t>(t) * d)[pair]);
+            ax += w * vv.x;
+            ay += w * vv.y;
+        }
+        partial[group * d + 2 * pair] = ax;
+        partial[group * d + 2 * pair + 1] = ay;
+    }
+    __syncthreads();
+    if (threadIdx.x < d) {
+        float total = 0.0f;
+        for (int g = 0; g < groups; ++g) total += partial[g * d + threadIdx.x];
+        p.out[head * d + threadIdx.x] = __float2half_rn(total / denom);
+    }
+}
+
+}  // namespace
+
+int launch_add_rmsnorm(const __half* stream_in, const __half* delta, const __half* weight, __half* stream_out,
+                       __half* normed, int hidden, float eps, cudaStream_t stream) {
+    add_rmsnorm_kernel<<<1, 256, static_cast<size_t>(hidden) * sizeof(__half), stream>>>(stream_in, delta, weight, stream_out,
+                                                                                       normed, hidden, eps);
+    if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    return W4A16_OK;
+}
+
+int launch_silu_mul(const __half* gate_up, __half* out, int inter, cudaStream_t stream) {
+    silu_mul_kernel<<<(inter + 255) / 256, 256, 0, stream>>>(gate_up, out, inter);
+    if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    return W4A16_OK;
+}
+
+int launch_attention_decode(const __half* qkv, __half* k_cache, __half* v_cache, __half* out, const long long* position,
+                            const float* inv_freq, int q_heads, int kv_heads, int head_dim, int max_len, float rope_scale,
+                            float softmax_scale, unsigned* status, cudaStream_t stream) {
+    AttentionParams params{qkv, k_cache, v_cache, out, position, inv_freq, q_heads, kv_heads, head_dim, max_len,
+                           rope_scale, softmax_scale, status};
+    const int pairs = head_dim / 2;
+    const int groups = 128 / pairs > 0 ? 128 / pairs : 1;
+    const size_t smem = (static_cast<size_t>(max_len) + head_dim + static_cast<size_t>(groups) * head_dim) * sizeof(float);
+    if (smem > 48 * 1024) {
+        static bool raised[64] = {};
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return W4A16_ERR_LAUNCH;
+        if (!raised[device]) {
+            if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+                return W4A16_ERR_LAUNCH;
+            }
+            raised[device] = true;
+        }
+        if (smem > 200 * 1024) return W4A16_ERR_TOO_LARGE;
+    }
+    attention_decode_kernel<<<q_heads, 128, smem, stream>>>(params);
+    if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    return W4A16_OK;
+}
+
+}  // namespace w4a16

@@ -1,0 +1,189 @@
+"""Batch-1 decode runner for LLaMA-architecture models whose linears are ``QuantizedLinear``.
+
+Replaces, for the decode step, what the reference gets from HuggingFace ``model.generate`` with a
+static cache (scripts/generate.py:260-365): one token is ``1 + 8 * layers + 3`` kernel launches --
+per block two add+RMSNorm, four W4A16 linears (q/k/v fused, o, gate/up fused, down), one attention
+kernel that also applies RoPE and appends to the cache, one SiLU*up -- captured once in a CUDA graph
+and replayed with the token and the position living in device memory.
+
+The arithmetic follows transformers' LlamaDecoderLayer rounding by rounding (FP16 residual sums,
+FP32 RMSNorm statistics, FP16 rotary products, FP32 softmax), so logits agree with the framework's
+eager forward up to summation order.  Prompts are consumed one token per step (no batched prefill).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _native
+from .fusion import FusedQuantizedLinear, FusedSlice, fuse_parallel_linears
+from .linear import QuantizedLinear
+
+
+def _ptr(tensor: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+
+
+def _check(status: int, what: str) -> None:
+    if status != 0:
+        raise RuntimeError(f"{what} failed: {_native.status_string(status)}")
+
+
+def add_rmsnorm(stream: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                normed: torch.Tensor) -> None:
+    """``stream += delta`` (FP16, in place; skipped when ``delta`` is None) and
+    ``normed = weight * half(stream * rsqrt(mean(stream^2) + eps))`` for one row."""
+    lib = _native.core()
+    _check(lib.w4a16_add_rmsnorm_f16(_ptr(stream), _ptr(delta), _ptr(weight), _ptr(stream), _ptr(normed),
+                                     stream.numel(), ctypes.c_float(eps),
+                                     ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "add_rmsnorm")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = half(silu(gate)) * up`` for ``gate_up = [gate | up]``."""
+    lib = _native.core()
+    _check(lib.w4a16_silu_mul_f16(_ptr(gate_up), _ptr(out), out.numel(),
+                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "silu_mul")
+
+
+def attention_decode(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                     position: torch.Tensor, inv_freq: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int,
+                     rope_scale: float, status: torch.Tensor) -> None:
+    """RoPE + cache append + attention of one token over ``[0, position]``; caches are ``[kv_heads, max_len, d]``."""
+    lib = _native.core()
+    _check(lib.w4a16_attention_decode_f16(
+        _ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(position), _ptr(inv_freq), q_heads, kv_heads, head_dim,
+        k_cache.shape[-2], ctypes.c_float(rope_scale), ctypes.c_float(head_dim ** -0.5), _ptr(status),
+        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "attention_decode")
+
+
+def _owner_of(parent: torch.nn.Module, names: tuple[str, ...]) -> QuantizedLinear:
+    """The fused layer behind sibling slices (they must all come from one fused launch, in order)."""
+    slices = [getattr(parent, name) for name in names]
+    if not all(isinstance(s, FusedSlice) for s in slices):
+        raise TypeError(f"{names} must be fused QuantizedLinear siblings (run fuse_parallel_linears first)")
+    owner = slices[0]._owner
+    if any(s._owner is not owner for s in slices) or [s.index for s in slices] != list(range(len(slices))):
+        raise ValueError(f"{names} are not the consecutive slices of one fused layer")
+    if len(owner.split_sizes) != len(names):
+        raise ValueError(f"the fused layer behind {names} has other members too")
+    return owner
+
+
+class LlamaDecodeRunner:
+    """Greedy batch-1 generation for a ``LlamaForCausalLM``-shaped model with W4A16 linears.
+
+    ``model`` keeps ownership of the weights; the runner fuses q/k/v and gate/up (if not fused yet),
+    allocates its own KV caches ``[layers, kv_heads, max_len, head_dim]`` and work buffers, and
+    captures the step in a CUDA graph at the first ``step``.
+    """
+
+    def __init__(self, model: torch.nn.Module, max_len: int):
+        config = model.config
+        self.hidden = config.hidden_size
+        self.q_heads = config.num_attention_heads
+        self.kv_heads = config.num_key_value_heads
+        self.head_dim = getattr(config, "head_dim", None) or self.hidden // self.q_heads
+        self.eps = float(config.rms_norm_eps)
+        self.max_len = int(max_len)
+        if self.head_dim not in (64, 128):
+            raise ValueError("the attention kernel supports head_dim 64 and 128")
+        body = model.model
+        fuse_parallel_linears(model)
+        self.embed = body.embed_tokens.weight
+        device = self.embed.device
+        if device.type != "cuda" or self.embed.dtype != torch.float16:
+            raise ValueError("the model must be an FP16 model on a CUDA device")
+        self.layers = []
+        for layer in body.layers:
+            attn, mlp = layer.self_attn, layer.mlp
+            entry = {
+                "norm1": layer.input_layernorm.weight, "qkv": _owner_of(attn, ("q_proj", "k_proj", "v_proj")),
+                "o": attn.o_proj, "norm2": layer.post_attention_layernorm.weight,
+                "gate_up": _owner_of(mlp, ("gate_proj", "up_proj")), "down": mlp.down_proj,
+            }
+            for key in ("o", "down"):
+                if not isinstance(entry[key], QuantizedLinear):
+                    raise TypeError("o_proj and down_proj must be QuantizedLinear layers")
+            self.layers.append(entry)
+        self.final_norm = body.norm.weight
+        self.lm_head = model.lm_head
+        rotary = body.rotary_emb
+        self.inv_freq = rotary.inv_freq.detach().to(device=device, dtype=torch.float32).contiguous()
+        self.rope_scale = float(getattr(rotary, "attention_scaling", 1.0))
+        self.inter = self.layers[0]["gate_up"].out_features // 2
+        n_layers = len(self.layers)
+        half = dict(dtype=torch.float16, device=device)
+        self.k_cache = torch.zeros((n_layers, self.kv_heads, self.max_len, self.head_dim), **half)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        self.token = torch.zeros((1,), dtype=torch.long, device=device)
+        self.position = torch.zeros((1,), dtype=torch.long, device=device)
+        self.status = torch.zeros((1,), dtype=torch.int32, device=device)
+        self.stream = torch.zeros((1, self.hidden), **half)
+        self.normed = torch.zeros((1, self.hidden), **half)
+        self.attn_out = torch.zeros((1, self.q_heads * self.head_dim), **half)
+        self.act = torch.zeros((1, self.inter), **half)
+        self.logits = None
+        self._graph = None
+        self.launches_per_step = 0
+
+    # ------------------------------------------------------------------ one token
+    def _enqueue_step(self) -> None:
+        torch.index_select(self.embed, 0, self.token, out=self.stream)
+        delta = None
+        for index, layer in enumerate(self.layers):
+            add_rmsnorm(self.stream, delta, layer["norm1"], self.eps, self.normed)
+            qkv = layer["qkv"](self.normed)
+            attention_decode(qkv, self.k_cache[index], self.v_cache[index], self.attn_out, self.position, self.inv_freq,
+                             self.q_heads, self.kv_heads, self.head_dim, self.rope_scale, self.status)
+            attn = layer["o"](self.attn_out)
+            add_rmsnorm(self.stream, attn, layer["norm2"], self.eps, self.normed)
+            gate_up = layer["gate_up"](self.normed)
+            silu_mul(gate_up, self.act)
+            delta = layer["down"](self.act)
+        add_rmsnorm(self.stream, delta, self.final_norm, self.eps, self.normed)
+        self.logits = self.lm_head(self.normed)
+        torch.argmax(self.logits, dim=-1, out=self.token)
+        self.position.add_(1)
+
+    def step(self) -> None:
+        """Consumes ``self.token`` at ``self.position``; leaves the greedy next token in ``self.token``."""
+        with torch.inference_mode():
+            if self._graph is None:
+                keep = (self.token.clone(), self.position.clone(), self.k_cache.clone(), self.v_cache.clone())
+                before = _native.core().w4a16_launch_count()
+                self._enqueue_step()                      # warm-up outside capture: workspaces, lazy initialisation
+                self.launches_per_step = _native.core().w4a16_launch_count() - before
+                torch.cuda.synchronize()
+                self.token.copy_(keep[0]); self.position.copy_(keep[1])
+                self.k_cache.copy_(keep[2]); self.v_cache.copy_(keep[3])
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self._enqueue_step()
+                self._graph = graph
+                self.token.copy_(keep[0]); self.position.copy_(keep[1])
+                self.k_cache.copy_(keep[2]); self.v_cache.copy_(keep[3])
+            self._graph.replay()
+
+    def reset(self) -> None:
+        self.position.zero_()
+        self.status.zero_()
+
+    def generate(self, prompt_ids: torch.Tensor, new_tokens: int) -> torch.Tensor:
+        """Greedy continuation of a 1-D prompt; returns the ``new_tokens`` generated ids."""
+        prompt = prompt_ids.reshape(-1).to(self.token.device)
+        if prompt.numel() + new_tokens > self.max_len:
+            raise ValueError("prompt + new tokens exceed the cache length")
+        self.reset()
+        out = torch.empty((new_tokens,), dtype=torch.long, device=self.token.device)
+        for i in range(prompt.numel()):
+            self.token.copy_(prompt[i:i + 1])
+            self.step()
+        for i in range(new_tokens):
+            out[i:i + 1].copy_(self.token)
+            if i + 1 < new_tokens:
+                self.step()
+        if int(self.status.item()) != 0:
+            raise RuntimeError("a decode step ran past the end of the KV cache")
+        return out
