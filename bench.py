@@ -406,6 +406,49 @@ def decode_bench(torch, device) -> dict:
     out["w4a16_programmatic_launch_fused_qkv_gate_up"] = measure("w4a16+pdl+fused q/k/v, gate/up")
     os.environ.pop("W4A16_PDL", None)
     out["w4a16_fused_qkv_gate_up"] = measure("w4a16+fused q/k/v, gate/up")
+
+    # this package's own decode step (nibble_b200/decode.py): same protocol, the prompt is consumed one
+    # token per step, so "prefill" here is 16 decode steps
+    from nibble_b200.decode import LlamaDecodeRunner
+
+    def measure_runner(label: str) -> dict:
+        runner = LlamaDecodeRunner(model, max_len=prompt_len + new_tokens + 8)
+        ids = prompt.reshape(-1)
+
+        def generate():
+            e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            runner.reset()
+            e0.record()
+            for i in range(prompt_len):
+                runner.token.copy_(ids[i:i + 1])
+                runner.step()
+            e1.record()
+            for _ in range(new_tokens - 1):
+                runner.step()
+            e2.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1), e0.elapsed_time(e2)
+
+        generate()
+        runs = [generate() for _ in range(5)]
+        prefill_ms = statistics.median(r[0] for r in runs)
+        total_ms = statistics.median(r[1] for r in runs)
+        decode_ms = total_ms - prefill_ms
+        row = {"decode_tok_s": round((new_tokens - 1) / decode_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
+               "ms_per_token": round(decode_ms / (new_tokens - 1), 4), "e2e_tok_s": round(new_tokens / total_ms * 1e3, 1),
+               "mode": "cuda_graph, own decode step", "kernels_per_token": runner.launches_per_step + 3,
+               "cache_overrun": int(runner.status.item())}
+        log(f"  decode {label}: {row}")
+        return row
+
+    try:
+        out["w4a16_decode_runner"] = measure_runner("w4a16 decode runner")
+        os.environ["W4A16_PDL"] = "1"
+        out["w4a16_decode_runner_programmatic_launch"] = measure_runner("w4a16 decode runner+pdl")
+        os.environ.pop("W4A16_PDL", None)
+    except Exception as error:
+        os.environ.pop("W4A16_PDL", None)
+        out["w4a16_decode_runner"] = {"error": repr(error)[:300]}
     if saved_pdl is not None:
         os.environ["W4A16_PDL"] = saved_pdl
     del model

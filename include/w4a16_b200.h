@@ -185,14 +185,16 @@ int w4a16_quantize_pack_f32(const void* weights, void* packed, void* scales,
  *   q and k, writes k and v into caches laid out [kv_heads][max_len][d], and writes
  *   softmax(q k^T * softmax_scale) v over positions 0..*position to out [q_heads*d].  d is 64 or
  *   128.  A position outside [0, max_len) sets *status to 1 and nothing is written.
+ * flags: W4A16_FLAG_PROGRAMMATIC_LAUNCH as for the linear (each kernel waits for its predecessor before
+ *   it reads or writes memory).
  */
 int w4a16_add_rmsnorm_f16(const void* stream_in, const void* delta, const void* weight, void* stream_out,
-                          void* normed, int64_t hidden, float eps, w4a16_stream_t stream);
-int w4a16_silu_mul_f16(const void* gate_up, void* out, int64_t intermediate, w4a16_stream_t stream);
+                          void* normed, int64_t hidden, float eps, uint32_t flags, w4a16_stream_t stream);
+int w4a16_silu_mul_f16(const void* gate_up, void* out, int64_t intermediate, uint32_t flags, w4a16_stream_t stream);
 int w4a16_attention_decode_f16(const void* qkv, void* k_cache, void* v_cache, void* out,
                                const int64_t* position, const float* inv_freq, int32_t q_heads,
                                int32_t kv_heads, int32_t head_dim, int32_t max_len, float rope_scale,
-                               float softmax_scale, uint32_t* status, w4a16_stream_t stream);
+                               float softmax_scale, uint32_t* status, uint32_t flags, w4a16_stream_t stream);
 
 /*
  * w4a16_linear_f16 for callers that cannot allocate device memory (no cudaMalloc after start-up,

@@ -67,12 +67,12 @@ C_API = {
     "w4a16_dequantize_f16": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
     "w4a16_quantize_pack_f16": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
     "w4a16_quantize_pack_f32": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
-    "w4a16_add_rmsnorm_f16": (ctypes.c_int, [_P, _P, _P, _P, _P, _I, ctypes.c_float, _P]),
-    "w4a16_silu_mul_f16": (ctypes.c_int, [_P, _P, _I, _P]),
+    "w4a16_add_rmsnorm_f16": (ctypes.c_int, [_P, _P, _P, _P, _P, _I, ctypes.c_float, ctypes.c_uint32, _P]),
+    "w4a16_silu_mul_f16": (ctypes.c_int, [_P, _P, _I, ctypes.c_uint32, _P]),
     "w4a16_attention_decode_f16": (
         ctypes.c_int,
         [_P, _P, _P, _P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_float,
-         ctypes.c_float, _P, _P],
+         ctypes.c_float, _P, ctypes.c_uint32, _P],
     ),
     "w4a16_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32)]),
     "w4a16_launch_count": (ctypes.c_uint64, []),

@@ -211,25 +211,27 @@ int w4a16_quantize_pack_f32(const void* weights, void* packed, void* scales, int
 }
 
 int w4a16_add_rmsnorm_f16(const void* stream_in, const void* delta, const void* weight, void* stream_out, void* normed,
-                          int64_t hidden, float eps, w4a16_stream_t stream) {
+                          int64_t hidden, float eps, uint32_t flags, w4a16_stream_t stream) {
     if (hidden <= 0 || hidden > 24576) return W4A16_ERR_BAD_SHAPE;
     if (stream_in == nullptr || weight == nullptr || normed == nullptr) return W4A16_ERR_NULL_POINTER;
     return w4a16::launch_add_rmsnorm(static_cast<const __half*>(stream_in), static_cast<const __half*>(delta),
                                      static_cast<const __half*>(weight), static_cast<__half*>(stream_out),
                                      static_cast<__half*>(normed), static_cast<int>(hidden), eps,
-                                     reinterpret_cast<cudaStream_t>(stream));
+                                     (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0, reinterpret_cast<cudaStream_t>(stream));
 }
 
-int w4a16_silu_mul_f16(const void* gate_up, void* out, int64_t intermediate, w4a16_stream_t stream) {
+int w4a16_silu_mul_f16(const void* gate_up, void* out, int64_t intermediate, uint32_t flags, w4a16_stream_t stream) {
     if (intermediate <= 0 || intermediate > (1 << 30)) return W4A16_ERR_BAD_SHAPE;
     if (gate_up == nullptr || out == nullptr) return W4A16_ERR_NULL_POINTER;
     return w4a16::launch_silu_mul(static_cast<const __half*>(gate_up), static_cast<__half*>(out),
-                                  static_cast<int>(intermediate), reinterpret_cast<cudaStream_t>(stream));
+                                  static_cast<int>(intermediate), (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0,
+                                  reinterpret_cast<cudaStream_t>(stream));
 }
 
 int w4a16_attention_decode_f16(const void* qkv, void* k_cache, void* v_cache, void* out, const int64_t* position,
                                const float* inv_freq, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_len,
-                               float rope_scale, float softmax_scale, uint32_t* status, w4a16_stream_t stream) {
+                               float rope_scale, float softmax_scale, uint32_t* status, uint32_t flags,
+                               w4a16_stream_t stream) {
     if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || (head_dim != 64 && head_dim != 128) || max_len <= 0) {
         return W4A16_ERR_BAD_SHAPE;
     }
@@ -241,7 +243,8 @@ int w4a16_attention_decode_f16(const void* qkv, void* k_cache, void* v_cache, vo
     return w4a16::launch_attention_decode(static_cast<const __half*>(qkv), static_cast<__half*>(k_cache),
                                           static_cast<__half*>(v_cache), static_cast<__half*>(out),
                                           reinterpret_cast<const long long*>(position), inv_freq, q_heads, kv_heads, head_dim,
-                                          max_len, rope_scale, softmax_scale, status, reinterpret_cast<cudaStream_t>(stream));
+                                          max_len, rope_scale, softmax_scale, status,
+                                          (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0, reinterpret_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -11,10 +11,16 @@
 // products and silu(gate) are each rounded to FP16 where the framework rounds them.
 //
 // The position is read from device memory, so one captured graph serves every step.
+//
+// Every kernel releases its successor at once (griddepcontrol.launch_dependents) and waits for its
+// predecessor (griddepcontrol.wait) before it touches memory: when launched with the programmatic
+// attribute, the next kernel's blocks are resident and -- for the linears -- already streaming weights
+// while this one computes.  Both instructions do nothing under an ordinary launch.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include "kernels.h"
+#include "unpack.cuh"
 
 namespace w4a16 {
 namespace {
@@ -49,6 +55,8 @@ add_rmsnorm_kernel(const __half* __restrict__ stream_in, const __half* __restric
                    __half* __restrict__ stream_out, __half* __restrict__ normed, int hidden, float eps) {
     __shared__ float scratch[8];
     extern __shared__ __half row[];        // the summed stream, kept for the second pass
+    pdl_release_downstream();
+    pdl_wait_for_upstream();
     float sq = 0.0f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         __half s = stream_in[i];
@@ -67,6 +75,8 @@ add_rmsnorm_kernel(const __half* __restrict__ stream_in, const __half* __restric
 
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ out, int inter) {
+    pdl_release_downstream();
+    pdl_wait_for_upstream();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= inter) return;
     const float g = __half2float(gate_up[i]);
@@ -96,6 +106,8 @@ attention_decode_kernel(const AttentionParams p) {
     const int d = p.head_dim;
     const int half_d = d >> 1;
     const int kv_head = head / (p.q_heads / p.kv_heads);
+    pdl_release_downstream();
+    pdl_wait_for_upstream();
     const long long pos = *p.position;
     if (pos < 0 || pos >= p.max_len) {
         if (threadIdx.x == 0) atomicMax(p.status, 1u);
@@ -184,27 +196,39 @@ attention_decode_kernel(const AttentionParams p) {
     }
 }
 
-}  // namespace
-
-int launch_add_rmsnorm(const __half* stream_in, const __half* delta, const __half* weight, __half* stream_out,
-                       __half* normed, int hidden, float eps, cudaStream_t stream) {
-    add_rmsnorm_kernel<<<1, 256, static_cast<size_t>(hidden) * sizeof(__half), stream>>>(stream_in, delta, weight, stream_out,
-                                                                                       normed, hidden, eps);
-    if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
+template <typename... Params, typename... Args>
+int launch_kernel(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, bool programmatic, cudaStream_t stream,
+                  Args... args) {
+    cudaLaunchConfig_t launch = {};
+    launch.gridDim = grid;
+    launch.blockDim = block;
+    launch.dynamicSmemBytes = smem;
+    launch.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    launch.attrs = attr;
+    launch.numAttrs = programmatic ? 1 : 0;
+    if (cudaLaunchKernelEx(&launch, kernel, static_cast<Params>(args)...) != cudaSuccess) return W4A16_ERR_LAUNCH;
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return W4A16_OK;
 }
 
-int launch_silu_mul(const __half* gate_up, __half* out, int inter, cudaStream_t stream) {
-    silu_mul_kernel<<<(inter + 255) / 256, 256, 0, stream>>>(gate_up, out, inter);
-    if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
-    g_launch_count.fetch_add(1, std::memory_order_relaxed);
-    return W4A16_OK;
+}  // namespace
+
+int launch_add_rmsnorm(const __half* stream_in, const __half* delta, const __half* weight, __half* stream_out,
+                       __half* normed, int hidden, float eps, bool programmatic, cudaStream_t stream) {
+    return launch_kernel(add_rmsnorm_kernel, dim3(1), dim3(256), static_cast<size_t>(hidden) * sizeof(__half), programmatic,
+                         stream, stream_in, delta, weight, stream_out, normed, hidden, eps);
+}
+
+int launch_silu_mul(const __half* gate_up, __half* out, int inter, bool programmatic, cudaStream_t stream) {
+    return launch_kernel(silu_mul_kernel, dim3((inter + 255) / 256), dim3(256), 0, programmatic, stream, gate_up, out, inter);
 }
 
 int launch_attention_decode(const __half* qkv, __half* k_cache, __half* v_cache, __half* out, const long long* position,
                             const float* inv_freq, int q_heads, int kv_heads, int head_dim, int max_len, float rope_scale,
-                            float softmax_scale, unsigned* status, cudaStream_t stream) {
+                            float softmax_scale, unsigned* status, bool programmatic, cudaStream_t stream) {
     AttentionParams params{qkv, k_cache, v_cache, out, position, inv_freq, q_heads, kv_heads, head_dim, max_len,
                            rope_scale, softmax_scale, status};
     const int pairs = head_dim / 2;
@@ -222,10 +246,7 @@ int launch_attention_decode(const __half* qkv, __half* k_cache, __half* v_cache,
         }
         if (smem > 200 * 1024) return W4A16_ERR_TOO_LARGE;
     }
-    attention_decode_kernel<<<q_heads, 128, smem, stream>>>(params);
-    if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
-    g_launch_count.fetch_add(1, std::memory_order_relaxed);
-    return W4A16_OK;
+    return launch_kernel(attention_decode_kernel, dim3(q_heads), dim3(128), smem, programmatic, stream, params);
 }
 
 }  // namespace w4a16

@@ -63,11 +63,11 @@ int launch_dequantize(const uint8_t* packed, const __half* scales, __half* weigh
 
 // Kernels either side of the linears in a LLaMA decode step (decode_ops.cu).
 int launch_add_rmsnorm(const __half* stream_in, const __half* delta, const __half* weight, __half* stream_out,
-                       __half* normed, int hidden, float eps, cudaStream_t stream);
-int launch_silu_mul(const __half* gate_up, __half* out, int inter, cudaStream_t stream);
+                       __half* normed, int hidden, float eps, bool programmatic, cudaStream_t stream);
+int launch_silu_mul(const __half* gate_up, __half* out, int inter, bool programmatic, cudaStream_t stream);
 int launch_attention_decode(const __half* qkv, __half* k_cache, __half* v_cache, __half* out, const long long* position,
                             const float* inv_freq, int q_heads, int kv_heads, int head_dim, int max_len, float rope_scale,
-                            float softmax_scale, unsigned* status, cudaStream_t stream);
+                            float softmax_scale, unsigned* status, bool programmatic, cudaStream_t stream);
 
 // Quantise + pack on the device (quantize.cu): FP16 or FP32 weights -> packed codes and FP16 scales.
 int launch_quantize_pack(const void* weights, bool is_f32, uint8_t* packed, __half* scales, int64_t N, int64_t K,

@@ -25,6 +25,12 @@ def _ptr(tensor: torch.Tensor | None) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
 
 
+def _flags() -> int:
+    from .cuda import programmatic_launch_enabled
+
+    return _native.FLAG_PROGRAMMATIC_LAUNCH if programmatic_launch_enabled() else 0
+
+
 def _check(status: int, what: str) -> None:
     if status != 0:
         raise RuntimeError(f"{what} failed: {_native.status_string(status)}")
@@ -36,14 +42,14 @@ def add_rmsnorm(stream: torch.Tensor, delta: torch.Tensor | None, weight: torch.
     ``normed = weight * half(stream * rsqrt(mean(stream^2) + eps))`` for one row."""
     lib = _native.core()
     _check(lib.w4a16_add_rmsnorm_f16(_ptr(stream), _ptr(delta), _ptr(weight), _ptr(stream), _ptr(normed),
-                                     stream.numel(), ctypes.c_float(eps),
+                                     stream.numel(), ctypes.c_float(eps), _flags(),
                                      ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "add_rmsnorm")
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     """``out = half(silu(gate)) * up`` for ``gate_up = [gate | up]``."""
     lib = _native.core()
-    _check(lib.w4a16_silu_mul_f16(_ptr(gate_up), _ptr(out), out.numel(),
+    _check(lib.w4a16_silu_mul_f16(_ptr(gate_up), _ptr(out), out.numel(), _flags(),
                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "silu_mul")
 
 
@@ -54,7 +60,7 @@ def attention_decode(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
     lib = _native.core()
     _check(lib.w4a16_attention_decode_f16(
         _ptr(qkv), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(position), _ptr(inv_freq), q_heads, kv_heads, head_dim,
-        k_cache.shape[-2], ctypes.c_float(rope_scale), ctypes.c_float(head_dim ** -0.5), _ptr(status),
+        k_cache.shape[-2], ctypes.c_float(rope_scale), ctypes.c_float(head_dim ** -0.5), _ptr(status), _flags(),
         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "attention_decode")
 
 
