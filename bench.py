@@ -411,8 +411,8 @@ def decode_bench(torch, device) -> dict:
     # token per step, so "prefill" here is 16 decode steps
     from nibble_b200.decode import LlamaDecodeRunner
 
-    def measure_runner(label: str) -> dict:
-        runner = LlamaDecodeRunner(model, max_len=prompt_len + new_tokens + 8)
+    def measure_runner(label: str, fuse_inputs: bool = True) -> dict:
+        runner = LlamaDecodeRunner(model, max_len=prompt_len + new_tokens + 8, fuse_inputs=fuse_inputs)
         ids = prompt.reshape(-1)
 
         def generate():
@@ -442,6 +442,7 @@ def decode_bench(torch, device) -> dict:
         return row
 
     try:
+        out["w4a16_decode_runner_separate_norm_and_silu_kernels"] = measure_runner("w4a16 decode runner, separate norm/silu kernels", False)
         out["w4a16_decode_runner"] = measure_runner("w4a16 decode runner")
         os.environ["W4A16_PDL"] = "1"
         out["w4a16_decode_runner_programmatic_launch"] = measure_runner("w4a16 decode runner+pdl")

@@ -172,6 +172,31 @@ int w4a16_quantize_pack_f32(const void* weights, void* packed, void* scales,
                             int64_t N, int64_t K, int64_t group_size, w4a16_stream_t stream);
 
 /*
+ * w4a16_linear_f16 whose activations are computed while they are staged on chip, so that the
+ * producer of x needs no kernel of its own (no counterpart in the reference):
+ *   W4A16_INPUT_SILU_MUL     x[m][k] = half(silu(g[m][k])) * u[m][k], where the `x` argument points at
+ *                            rows [g | u] of 2K values (the output of a fused gate/up projection);
+ *   W4A16_INPUT_ADD_RMSNORM  M must be 1; s = half(x + second) (second may be NULL),
+ *                            x'[k] = norm_weight[k] * half(float(s[k]) * rsqrt(mean(s^2) + eps)); s is also
+ *                            written to stream_out (K values; must not alias x or second) when non-NULL.
+ * Same arithmetic as w4a16_silu_mul_f16 / w4a16_add_rmsnorm_f16 followed by w4a16_linear_f16.
+ * Only the tensor-core path takes a transform: group_size 128 and 16-byte aligned x, packed, second,
+ * norm_weight and stream_out, M <= 64; otherwise W4A16_ERR_BAD_CONFIG.  transform == NULL is w4a16_linear_f16.
+ */
+enum { W4A16_INPUT_PLAIN = 0, W4A16_INPUT_SILU_MUL = 1, W4A16_INPUT_ADD_RMSNORM = 2 };
+typedef struct w4a16_input_transform {
+    int32_t kind;
+    const void* second;
+    const void* norm_weight;
+    void* stream_out;
+    float eps;
+} w4a16_input_transform;
+int w4a16_linear_f16_input(const void* x, const void* packed, const void* scales, void* y,
+                           int64_t M, int64_t N, int64_t K, int64_t group_size,
+                           void* workspace, size_t workspace_bytes, uint32_t flags,
+                           const w4a16_input_transform* transform, w4a16_stream_t stream);
+
+/*
  * The three kernels either side of the linears in one LLaMA decode step (batch 1), for a runner
  * that replaces the framework's decoder-layer code (the reference drives HuggingFace's
  * model.generate, scripts/generate.py:260-365; the arithmetic restated is transformers'

@@ -67,6 +67,7 @@ C_API = {
     "w4a16_dequantize_f16": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
     "w4a16_quantize_pack_f16": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
     "w4a16_quantize_pack_f32": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
+    "w4a16_linear_f16_input": (ctypes.c_int, [_P, _P, _P, _P, _I, _I, _I, _I, _P, ctypes.c_size_t, ctypes.c_uint32, _P, _P]),
     "w4a16_add_rmsnorm_f16": (ctypes.c_int, [_P, _P, _P, _P, _P, _I, ctypes.c_float, ctypes.c_uint32, _P]),
     "w4a16_silu_mul_f16": (ctypes.c_int, [_P, _P, _I, ctypes.c_uint32, _P]),
     "w4a16_attention_decode_f16": (
@@ -79,6 +80,16 @@ C_API = {
     "w4a16_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "w4a16_abi_version": (ctypes.c_int, []),
 }
+
+INPUT_PLAIN, INPUT_SILU_MUL, INPUT_ADD_RMSNORM = 0, 1, 2
+
+
+class InputTransform(ctypes.Structure):
+    """``w4a16_input_transform`` of include/w4a16_b200.h."""
+
+    _fields_ = [("kind", ctypes.c_int32), ("second", ctypes.c_void_p), ("norm_weight", ctypes.c_void_p),
+                ("stream_out", ctypes.c_void_p), ("eps", ctypes.c_float)]
+
 
 FLAG_PROGRAMMATIC_LAUNCH = 1 << 0
 FLAG_FORCE_GENERIC = 1 << 1

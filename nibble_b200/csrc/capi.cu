@@ -100,6 +100,33 @@ int w4a16_linear_f16(const void* x, const void* packed, const void* scales, void
     return launched;
 }
 
+int w4a16_linear_f16_input(const void* x, const void* packed, const void* scales, void* y, int64_t M, int64_t N,
+                           int64_t K, int64_t group_size, void* workspace, size_t workspace_bytes, uint32_t flags,
+                           const w4a16_input_transform* transform, w4a16_stream_t stream) {
+    if (transform == nullptr || transform->kind == W4A16_INPUT_PLAIN) {
+        return w4a16_linear_f16(x, packed, scales, y, M, N, K, group_size, workspace, workspace_bytes, flags, stream);
+    }
+    const int status = validate_linear(x, packed, scales, y, M, N, K, group_size);
+    if (status != W4A16_OK || M == 0 || N == 0) return status;
+    if (K == 0 || M > 64 || !fast_path_applies(x, packed, K, group_size)) return W4A16_ERR_BAD_CONFIG;
+    w4a16::LinearProblem p{static_cast<const __half*>(x), static_cast<const uint8_t*>(packed),
+                           static_cast<const __half*>(scales), y, M, N, K, group_size,
+                           workspace, workspace_bytes, nullptr, transform};
+    int max_splits = 1;
+    if (workspace != nullptr && aligned16(workspace)) {
+        for (int splits = w4a16::kMaxKSplits; splits > 1; splits >>= 1) {
+            if (workspace_bytes >= w4a16::linear_workspace_bytes_for(M, N, splits)) {
+                max_splits = splits;
+                break;
+            }
+        }
+    }
+    w4a16_linear_config cfg = w4a16::choose_linear_config(M, N, K, max_splits);
+    if (reinterpret_cast<uintptr_t>(scales) % 4 != 0) cfg.unroll = 1;
+    return w4a16::launch_linear_mma(p, cfg, (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0,
+                                    (flags & W4A16_FLAG_OUTPUT_F32) != 0, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int w4a16_linear_f16_config(const void* x, const void* packed, const void* scales, void* y, int64_t M,
                             int64_t N, int64_t K, int64_t group_size, void* workspace,
                             size_t workspace_bytes, uint32_t flags, const w4a16_linear_config* config,

@@ -28,6 +28,7 @@ struct LinearProblem {
     void* workspace;          // may be null
     size_t workspace_bytes;
     const w4a16_peer_target* peers = nullptr;   // fan the result out to a tensor-parallel group
+    const w4a16_input_transform* input = nullptr;   // x is derived from other buffers while it is staged
 };
 
 // Workspace layout for split-K: arrival counters first, FP32 partials after them.

@@ -74,7 +74,47 @@ struct MmaParams {
     long long col_out;              // first column this rank writes there
     long long wait_polls;           // > 0: also wait (bounded) for every rank's publication of this epoch
     int rank, world;
+    // Activations derived while they are staged (W4A16_INPUT_*): see the staging code.
+    int x_mode;
+    long long x_ld;                 // elements between batch rows of x (2K for [gate | up] rows)
+    const __half* x_second;         // delta of the residual stream, or null
+    const __half* norm_weight;
+    __half* stream_out;
+    float eps;
 };
+
+// Eight FP16 values at once.
+struct Half8 {
+    __half2 v[4];
+};
+__device__ __forceinline__ Half8 as_half8(const uint4& q) {
+    Half8 h;
+    h.v[0] = *reinterpret_cast<const __half2*>(&q.x);
+    h.v[1] = *reinterpret_cast<const __half2*>(&q.y);
+    h.v[2] = *reinterpret_cast<const __half2*>(&q.z);
+    h.v[3] = *reinterpret_cast<const __half2*>(&q.w);
+    return h;
+}
+__device__ __forceinline__ uint4 as_uint4(const Half8& h) {
+    uint4 q;
+    q.x = *reinterpret_cast<const uint32_t*>(&h.v[0]);
+    q.y = *reinterpret_cast<const uint32_t*>(&h.v[1]);
+    q.z = *reinterpret_cast<const uint32_t*>(&h.v[2]);
+    q.w = *reinterpret_cast<const uint32_t*>(&h.v[3]);
+    return q;
+}
+// half(silu(g)) * u, elementwise, rounded as a framework rounds it: silu in FP32, to FP16, then an FP16 product
+__device__ __forceinline__ uint4 silu_mul8(const uint4& gate, const uint4& up) {
+    const Half8 g = as_half8(gate), u = as_half8(up);
+    Half8 out;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(g.v[i]);
+        const __half2 act = __floats2half2_rn(f.x / (1.0f + expf(-f.x)), f.y / (1.0f + expf(-f.y)));
+        out.v[i] = __hmul2(act, u.v[i]);
+    }
+    return as_uint4(out);
+}
 
 // Bounded wait until flags[sender] has reached `epoch` for every sender; a sender that never arrives
 // is recorded in *status (sender + 1) and the wait moves on.
@@ -304,20 +344,77 @@ linear_mma_kernel(const MmaParams p) {
     // 16-byte unit ((c * 4 + i) * XB + n) * 4 + t holds, for batch row n, the eight activations
     // k = c*128 + t*32 + i*8 .. +8 re-paired as (x0,x4)(x1,x5)(x2,x6)(x3,x7).  Rows past the batch
     // repeat its last row: their products land in output columns that are never stored.
+    // With p.x_mode set, the activations are computed here from what produced them: silu(gate) * up of
+    // a fused gate/up output, or the RMSNorm of the residual stream plus the last block's output (one
+    // CTA also writes the summed stream back).
     {
         const int units_per_row = span * 16;   // 16-byte pieces of one batch row in this K slice
-        for (int n = 0; n < XB; ++n) {
-            const int src_row = m0 + min(n, batch_here - 1);
-            const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(src_row) * p.K +
-                                                              static_cast<size_t>(c_begin) * kGroup);
+        auto put = [&](const uint4& q, int j, int n) {
+            const int c = j >> 4, tt = (j >> 2) & 3, i = j & 3;
+            const unsigned dst = xs + (((c * 4 + i) * XB + n) * 4 + tt) * 16;
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(prmt(q.x, q.z, 0x5410u)),
+                         "r"(prmt(q.x, q.z, 0x7632u)), "r"(prmt(q.y, q.w, 0x5410u)),
+                         "r"(prmt(q.y, q.w, 0x7632u))
+                         : "memory");
+        };
+        if (p.x_mode == W4A16_INPUT_ADD_RMSNORM) {
+            // pass 1, whole row: s = half(stream + delta), sum of squares in FP32
+            const uint4* s_in = reinterpret_cast<const uint4*>(p.x);
+            const uint4* d_in = reinterpret_cast<const uint4*>(p.x_second);
+            const bool writer = p.stream_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+            auto summed = [&](int j) {
+                Half8 s8 = as_half8(ldg_keep16(s_in + j));
+                if (d_in != nullptr) {
+                    const Half8 d8 = as_half8(ldg_keep16(d_in + j));
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) s8.v[i] = __hadd2(s8.v[i], d8.v[i]);
+                }
+                return s8;
+            };
+            float sq = 0.0f;
+            for (int j = tid; j < (p.K >> 3); j += kThreads) {
+                const Half8 s8 = summed(j);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __half22float2(s8.v[i]);
+                    sq += f.x * f.x + f.y * f.y;
+                }
+                if (writer) reinterpret_cast<uint4*>(p.stream_out)[j] = as_uint4(s8);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            float* scratch = reinterpret_cast<float*>(smem + 64);     // second half of the flag header: free until the epilogue
+            if (lane == 0) scratch[warp] = sq;
+            __syncthreads();
+            float total = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kWarpsPerCta; ++w) total += scratch[w];
+            const float inv = rsqrtf(total / static_cast<float>(p.K) + p.eps);
+            // pass 2, this CTA's K slice: weight * half(s * inv)
+            const uint4* w_in = reinterpret_cast<const uint4*>(p.norm_weight);
             for (int j = tid; j < units_per_row; j += kThreads) {
-                const uint4 q = ldg_keep16(src + j);
-                const int c = j >> 4, tt = (j >> 2) & 3, i = j & 3;
-                const unsigned dst = xs + (((c * 4 + i) * XB + n) * 4 + tt) * 16;
-                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(prmt(q.x, q.z, 0x5410u)),
-                             "r"(prmt(q.x, q.z, 0x7632u)), "r"(prmt(q.y, q.w, 0x5410u)),
-                             "r"(prmt(q.y, q.w, 0x7632u))
-                             : "memory");
+                const int at = c_begin * 16 + j;
+                const Half8 s8 = summed(at);
+                const Half8 w8 = as_half8(ldg_keep16(w_in + at));
+                Half8 x8;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __half22float2(s8.v[i]);
+                    x8.v[i] = __hmul2(w8.v[i], __floats2half2_rn(f.x * inv, f.y * inv));
+                }
+                put(as_uint4(x8), j, 0);
+            }
+        } else {
+            for (int n = 0; n < XB; ++n) {
+                const int src_row = m0 + min(n, batch_here - 1);
+                const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(src_row) * p.x_ld +
+                                                                  static_cast<size_t>(c_begin) * kGroup);
+                if (p.x_mode == W4A16_INPUT_SILU_MUL) {
+                    const uint4* up = src + (p.K >> 3);              // the second K values of the row
+                    for (int j = tid; j < units_per_row; j += kThreads) put(silu_mul8(ldg_keep16(src + j), ldg_keep16(up + j)), j, n);
+                } else {
+                    for (int j = tid; j < units_per_row; j += kThreads) put(ldg_keep16(src + j), j, n);
+                }
             }
         }
     }
@@ -957,6 +1054,31 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
     params.col_out = 0;
     params.rank = 0;
     params.world = 1;
+    params.x_mode = W4A16_INPUT_PLAIN;
+    params.x_ld = prob.K;
+    params.x_second = nullptr;
+    params.norm_weight = nullptr;
+    params.stream_out = nullptr;
+    params.eps = 0.0f;
+    if (prob.input != nullptr && prob.input->kind != W4A16_INPUT_PLAIN) {
+        const w4a16_input_transform& in = *prob.input;
+        auto aligned = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
+        if (in.kind == W4A16_INPUT_SILU_MUL) {
+            params.x_ld = 2 * prob.K;
+        } else if (in.kind == W4A16_INPUT_ADD_RMSNORM) {
+            if (prob.M != 1) return W4A16_ERR_BAD_SHAPE;
+            if (in.norm_weight == nullptr) return W4A16_ERR_NULL_POINTER;
+            if (!aligned(in.second) || !aligned(in.norm_weight) || !aligned(in.stream_out)) return W4A16_ERR_MISALIGNED;
+            if (in.stream_out != nullptr && (in.stream_out == prob.x || in.stream_out == in.second)) return W4A16_ERR_BAD_CONFIG;
+            params.x_second = static_cast<const __half*>(in.second);
+            params.norm_weight = static_cast<const __half*>(in.norm_weight);
+            params.stream_out = static_cast<__half*>(in.stream_out);
+            params.eps = in.eps;
+        } else {
+            return W4A16_ERR_BAD_CONFIG;
+        }
+        params.x_mode = in.kind;
+    }
     if (prob.peers != nullptr) {
         const w4a16_peer_target& t = *prob.peers;
         if (t.outputs == nullptr || t.flags == nullptr || t.done_counter == nullptr || t.send_epoch == nullptr ||

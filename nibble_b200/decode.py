@@ -2,9 +2,11 @@
 
 Replaces, for the decode step, what the reference gets from HuggingFace ``model.generate`` with a
 static cache (scripts/generate.py:260-365): one token is ``1 + 8 * layers + 3`` kernel launches --
-per block two add+RMSNorm, four W4A16 linears (q/k/v fused, o, gate/up fused, down), one attention
-kernel that also applies RoPE and appends to the cache, one SiLU*up -- captured once in a CUDA graph
-and replayed with the token and the position living in device memory.
+per block four W4A16 linears (q/k/v fused, o, gate/up fused, down) and one attention kernel that also
+applies RoPE and appends to the cache; the two add+RMSNorm and the SiLU*up of a block are computed
+inside the linears that consume them, while those stage their activations (``fuse_inputs``; without
+it they are three more small kernels per block).  The step is captured once in a CUDA graph and
+replayed with the token and the position living in device memory.
 
 The arithmetic follows transformers' LlamaDecoderLayer rounding by rounding (FP16 residual sums,
 FP32 RMSNorm statistics, FP16 rotary products, FP32 softmax), so logits agree with the framework's
@@ -64,6 +66,19 @@ def attention_decode(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "attention_decode")
 
 
+def linear_with_input(layer: QuantizedLinear, x: torch.Tensor, out: torch.Tensor, workspace: torch.Tensor,
+                      transform: "_native.InputTransform | None") -> None:
+    """``out = layer(x')`` through the C ABI, ``x'`` being ``x`` or what ``transform`` derives from it
+    on chip (see ``w4a16_linear_f16_input``).  ``layer`` must have 128-wide groups and no bias."""
+    lib = _native.core()
+    rows = out.shape[0]
+    _check(lib.w4a16_linear_f16_input(
+        _ptr(x), _ptr(layer.packed_weights), _ptr(layer.scales), _ptr(out), rows, layer.out_features, layer.in_features,
+        layer.group_size, _ptr(workspace), workspace.numel(), _flags(),
+        None if transform is None else ctypes.byref(transform),
+        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "linear_with_input")
+
+
 def _owner_of(parent: torch.nn.Module, names: tuple[str, ...]) -> QuantizedLinear:
     """The fused layer behind sibling slices (they must all come from one fused launch, in order)."""
     slices = [getattr(parent, name) for name in names]
@@ -85,7 +100,7 @@ class LlamaDecodeRunner:
     captures the step in a CUDA graph at the first ``step``.
     """
 
-    def __init__(self, model: torch.nn.Module, max_len: int):
+    def __init__(self, model: torch.nn.Module, max_len: int, fuse_inputs: bool | None = None):
         config = model.config
         self.hidden = config.hidden_size
         self.q_heads = config.num_attention_heads
@@ -133,9 +148,47 @@ class LlamaDecodeRunner:
         self.logits = None
         self._graph = None
         self.launches_per_step = 0
+        linears = [entry[key] for entry in self.layers for key in ("qkv", "o", "gate_up", "down")] + [self.lm_head]
+        can_fuse = all(isinstance(m, QuantizedLinear) and m.group_size == 128 and m.bias is None for m in linears)
+        if fuse_inputs and not can_fuse:
+            raise ValueError("fuse_inputs needs every linear to be a bias-free QuantizedLinear with group_size 128")
+        self.fuse_inputs = can_fuse if fuse_inputs is None else bool(fuse_inputs)
+        if self.fuse_inputs:
+            self.stream_b = torch.zeros_like(self.stream)
+            self.qkv_out = torch.zeros((1, self.layers[0]["qkv"].out_features), **half)
+            self.o_out = torch.zeros((1, self.hidden), **half)
+            self.gate_up_out = torch.zeros((1, 2 * self.inter), **half)
+            self.down_out = torch.zeros((1, self.hidden), **half)
+            self.logits = torch.zeros((1, self.lm_head.out_features), **half)
+            self.workspace = torch.zeros((8 << 20,), dtype=torch.uint8, device=device)   # split-K scratch; kernels leave it zeroed
 
     # ------------------------------------------------------------------ one token
+    def _norm_into(self, source: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
+                   target: torch.Tensor | None) -> "_native.InputTransform":
+        return _native.InputTransform(_native.INPUT_ADD_RMSNORM, 0 if delta is None else delta.data_ptr(), weight.data_ptr(),
+                                      0 if target is None else target.data_ptr(), self.eps)
+
+    def _enqueue_fused_step(self) -> None:
+        a, b, ws = self.stream, self.stream_b, self.workspace
+        silu = _native.InputTransform(_native.INPUT_SILU_MUL, 0, 0, 0, 0.0)
+        torch.index_select(self.embed, 0, self.token, out=a)
+        delta = None
+        for index, layer in enumerate(self.layers):
+            linear_with_input(layer["qkv"], a, self.qkv_out, ws, self._norm_into(a, delta, layer["norm1"], b))
+            attention_decode(self.qkv_out, self.k_cache[index], self.v_cache[index], self.attn_out, self.position,
+                             self.inv_freq, self.q_heads, self.kv_heads, self.head_dim, self.rope_scale, self.status)
+            linear_with_input(layer["o"], self.attn_out, self.o_out, ws, None)
+            linear_with_input(layer["gate_up"], b, self.gate_up_out, ws, self._norm_into(b, self.o_out, layer["norm2"], a))
+            linear_with_input(layer["down"], self.gate_up_out, self.down_out, ws, silu)
+            delta = self.down_out
+        linear_with_input(self.lm_head, a, self.logits, ws, self._norm_into(a, delta, self.final_norm, None))
+        torch.argmax(self.logits, dim=-1, out=self.token)
+        self.position.add_(1)
+
     def _enqueue_step(self) -> None:
+        if self.fuse_inputs:
+            self._enqueue_fused_step()
+            return
         torch.index_select(self.embed, 0, self.token, out=self.stream)
         delta = None
         for index, layer in enumerate(self.layers):

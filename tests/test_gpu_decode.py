@@ -92,6 +92,59 @@ def test_attention_decode_matches_rope_plus_sdpa(q_heads, kv_heads, head_dim):
     assert status.item() == 1
 
 
+def test_linear_with_fused_input_equals_the_separate_kernels():
+    import ctypes
+
+    from nibble_b200 import _native, quantize_and_pack_weights
+    from nibble_b200.decode import add_rmsnorm, linear_with_input, silu_mul
+    from nibble_b200.linear import QuantizedLinear
+
+    g = torch.Generator().manual_seed(11)
+    workspace = torch.zeros((8 << 20,), dtype=torch.uint8, device="cuda")
+    for hidden, n in ((2048, 2560), (2048, 11264), (2048, 32000), (8192, 1024)):
+        packed, scales = quantize_and_pack_weights((torch.randn((n, hidden), generator=g) * 0.02).cuda(), 128)
+        layer = QuantizedLinear(packed, scales, 128)
+        stream = torch.randn((1, hidden), generator=g).half().cuda()
+        delta = torch.randn((1, hidden), generator=g).half().cuda()
+        weight = (torch.randn((hidden,), generator=g) * 0.1 + 1).half().cuda()
+        for second in (delta, None):
+            want_stream, normed = stream.clone(), torch.empty_like(stream)
+            add_rmsnorm(want_stream, second, weight, 1e-5, normed)
+            want = torch.empty((1, n), dtype=torch.float16, device="cuda")
+            linear_with_input(layer, normed, want, workspace, None)
+            got, new_stream = torch.empty_like(want), torch.zeros_like(stream)
+            transform = _native.InputTransform(_native.INPUT_ADD_RMSNORM, 0 if second is None else second.data_ptr(),
+                                               weight.data_ptr(), new_stream.data_ptr(), 1e-5)
+            linear_with_input(layer, stream, got, workspace, transform)
+            assert torch.equal(new_stream, want_stream)
+            torch.testing.assert_close(got, want, rtol=2e-3, atol=2e-3)   # the sum of squares is taken in another order
+            again = torch.empty_like(got)
+            linear_with_input(layer, stream, again, workspace, transform)  # the split-K scratch is reusable as it was left
+            assert torch.equal(again, got)
+    for inter, n in ((5632, 2048), (28672, 1024)):
+        packed, scales = quantize_and_pack_weights((torch.randn((n, inter), generator=g) * 0.02).cuda(), 128)
+        layer = QuantizedLinear(packed, scales, 128)
+        for rows in (1, 3):
+            gate_up = (torch.randn((rows, 2 * inter), generator=g) * 2).half().cuda()
+            act = torch.empty((rows, inter), dtype=torch.float16, device="cuda")
+            for r in range(rows):
+                silu_mul(gate_up[r:r + 1], act[r:r + 1])
+            want, got = (torch.empty((rows, n), dtype=torch.float16, device="cuda") for _ in range(2))
+            linear_with_input(layer, act, want, workspace, None)
+            linear_with_input(layer, gate_up, got, workspace, _native.InputTransform(_native.INPUT_SILU_MUL, 0, 0, 0, 0.0))
+            assert torch.equal(got, want)                                 # same values staged, same kernel
+    # refusals: RMSNorm input is for one row; the stream may not be updated in place
+    lib = _native.core()
+    bad = _native.InputTransform(_native.INPUT_ADD_RMSNORM, 0, weight.data_ptr(), stream.data_ptr(), 1e-5)
+    out = torch.empty((1, n), dtype=torch.float16, device="cuda")
+    args = lambda rows, t: (stream.data_ptr(), packed.data_ptr(), scales.data_ptr(), out.data_ptr(), rows, n, inter, 128,
+                            None, 0, 0, ctypes.byref(t), None)
+    assert lib.w4a16_linear_f16_input(*args(1, bad)) == -6
+    ok = _native.InputTransform(_native.INPUT_ADD_RMSNORM, 0, weight.data_ptr(), 0, 1e-5)
+    assert lib.w4a16_linear_f16_input(*args(2, ok)) == -2
+    torch.cuda.synchronize()
+
+
 def test_runner_logits_follow_the_framework_forward():
     from transformers import StaticCache
 
@@ -113,19 +166,20 @@ def test_runner_logits_follow_the_framework_forward():
             out = model(input_ids=tokens[t].view(1, 1), past_key_values=cache,
                         cache_position=torch.tensor([t], device="cuda"), use_cache=True)
             want.append(out.logits[0, -1].float().clone())
-    runner = LlamaDecodeRunner(model, max_len=32)
-    assert runner.launches_per_step == 0
-    worst = 0.0
-    for t in range(tokens.numel()):
-        runner.token.copy_(tokens[t:t + 1])
-        runner.step()
-        got = runner.logits[0].float()
-        scale = want[t].abs().max().item()
-        worst = max(worst, (got - want[t]).abs().max().item() / scale)
-        assert int(runner.position.item()) == t + 1
-    assert runner.launches_per_step == 8 * 3 + 2          # our kernels per token: 8 per block, final norm, lm_head
-    assert worst < 2e-2, worst
-    assert runner.status.item() == 0
+    for fuse_inputs, per_block, tail in ((False, 8, 2), (True, 5, 1)):
+        runner = LlamaDecodeRunner(model, max_len=32, fuse_inputs=fuse_inputs)
+        assert runner.launches_per_step == 0
+        worst = 0.0
+        for t in range(tokens.numel()):
+            runner.token.copy_(tokens[t:t + 1])
+            runner.step()
+            got = runner.logits[0].float()
+            scale = want[t].abs().max().item()
+            worst = max(worst, (got - want[t]).abs().max().item() / scale)
+            assert int(runner.position.item()) == t + 1
+        assert runner.launches_per_step == per_block * 3 + tail     # our kernels per token
+        assert worst < 2e-2, worst
+        assert runner.status.item() == 0
 
 
 def test_generate_is_repeatable_and_checks_the_cache_length():
