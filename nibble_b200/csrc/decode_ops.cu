@@ -97,14 +97,22 @@ struct AttentionParams {
     unsigned* status;         // set to 1 when the position does not fit the cache
 };
 
-// One CTA per query head, 128 threads, head_dim 64 or 128.
+// One CTA per query head, 128 threads.  D/8 consecutive lanes share a cached position: each reads 16
+// bytes of its K (then V) row, so a row is one coalesced 128- or 256-byte read, and the 128 threads
+// cover 16 (D = 64) or 8 (D = 128) positions per pass with independent loads in flight.
+template <int D>
 __global__ void __launch_bounds__(128)
 attention_decode_kernel(const AttentionParams p) {
-    extern __shared__ float scores[];                 // max_len floats, then q (head_dim floats), then partial sums
+    constexpr int kLanesPerPos = D / 8;
+    constexpr int kPosPerPass = 128 / kLanesPerPos;
+    extern __shared__ float scores[];                 // max_len floats
     __shared__ float scratch[4];
+    __shared__ float q[D];
+    __shared__ __align__(16) __half k_new[D];
+    __shared__ __align__(16) __half v_new[D];
+    __shared__ float partial[kPosPerPass][D];
     const int head = blockIdx.x;
-    const int d = p.head_dim;
-    const int half_d = d >> 1;
+    constexpr int half_d = D / 2;
     const int kv_head = head / (p.q_heads / p.kv_heads);
     pdl_release_downstream();
     pdl_wait_for_upstream();
@@ -113,20 +121,18 @@ attention_decode_kernel(const AttentionParams p) {
         if (threadIdx.x == 0) atomicMax(p.status, 1u);
         return;
     }
-    float* q = scores + p.max_len;
-    float* partial = q + d;                           // [4][d]
-    __shared__ __half k_new[128], v_new[128];
-
-    const __half* q_in = p.qkv + head * d;
-    const __half* k_in = p.qkv + p.q_heads * d + kv_head * d;
-    const __half* v_in = p.qkv + (p.q_heads + p.kv_heads) * d + kv_head * d;
+    const __half* q_in = p.qkv + head * D;
+    const __half* k_in = p.qkv + p.q_heads * D + kv_head * D;
+    const __half* v_in = p.qkv + (p.q_heads + p.kv_heads) * D + kv_head * D;
     // rotary embedding, rounded as the framework rounds it: cos/sin to FP16, two FP16 products, one FP16 sum
-    if (threadIdx.x < d) {
+    if (threadIdx.x < D) {
         const int i = threadIdx.x;
         const int f = i < half_d ? i : i - half_d;
         const float angle = static_cast<float>(pos) * p.inv_freq[f];
-        const __half c = __float2half_rn(cosf(angle) * p.rope_scale);
-        const __half s = __float2half_rn(sinf(angle) * p.rope_scale);
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        const __half c = __float2half_rn(cs * p.rope_scale);
+        const __half s = __float2half_rn(sn * p.rope_scale);
         const __half q_rot = i < half_d ? __hneg(q_in[i + half_d]) : q_in[i - half_d];
         const __half k_rot = i < half_d ? __hneg(k_in[i + half_d]) : k_in[i - half_d];
         // the _rn forms are never contracted into one fused multiply-add: two roundings, then a third
@@ -135,64 +141,80 @@ attention_decode_kernel(const AttentionParams p) {
         k_new[i] = k_val;
         v_new[i] = v_in[i];
         if (head % (p.q_heads / p.kv_heads) == 0) {   // one CTA per KV head appends to the cache
-            p.k_cache[(static_cast<size_t>(kv_head) * p.max_len + pos) * d + i] = k_val;
-            p.v_cache[(static_cast<size_t>(kv_head) * p.max_len + pos) * d + i] = v_in[i];
+            p.k_cache[(static_cast<size_t>(kv_head) * p.max_len + pos) * D + i] = k_val;
+            p.v_cache[(static_cast<size_t>(kv_head) * p.max_len + pos) * D + i] = v_in[i];
         }
     }
     __syncthreads();
 
     const int length = static_cast<int>(pos) + 1;
-    const __half* k_base = p.k_cache + static_cast<size_t>(kv_head) * p.max_len * d;
-    const __half* v_base = p.v_cache + static_cast<size_t>(kv_head) * p.max_len * d;
-    // scores: one thread per cached position (the newest comes from shared memory, not from the cache,
-    // because another CTA writes it)
+    const int sub = threadIdx.x % kLanesPerPos;       // which 8 of the D dims
+    const int slot = threadIdx.x / kLanesPerPos;      // which position of a pass
+    const uint4* k_rows = reinterpret_cast<const uint4*>(p.k_cache + static_cast<size_t>(kv_head) * p.max_len * D) + sub;
+    const uint4* v_rows = reinterpret_cast<const uint4*>(p.v_cache + static_cast<size_t>(kv_head) * p.max_len * D) + sub;
+    // The newest position comes from shared memory, not from the cache: another CTA writes it there.
+    auto row_piece = [&](const uint4* rows, const __half* newest, int t) {
+        return t == length - 1 ? reinterpret_cast<const uint4*>(newest)[sub] : rows[static_cast<size_t>(t) * kLanesPerPos];
+    };
+    float qf[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qf[i] = q[sub * 8 + i];
+
     float local_max = -INFINITY;
-    for (int t = threadIdx.x; t < length; t += blockDim.x) {
+#pragma unroll 4
+    for (int base = 0; base < length; base += kPosPerPass) {
+        const int t = base + slot;
         float dot = 0.0f;
-        if (t == length - 1) {
-            for (int i = 0; i < d; ++i) dot += q[i] * __half2float(k_new[i]);
-        } else {
-            const __half2* k_row = reinterpret_cast<const __half2*>(k_base + static_cast<size_t>(t) * d);
-            for (int i = 0; i < half_d; ++i) {
-                const float2 kk = __half22float2(k_row[i]);
-                dot += q[2 * i] * kk.x + q[2 * i + 1] * kk.y;
+        if (t < length) {
+            const uint4 piece = row_piece(k_rows, k_new, t);
+            const __half2* h = reinterpret_cast<const __half2*>(&piece);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 kk = __half22float2(h[i]);
+                dot += qf[2 * i] * kk.x + qf[2 * i + 1] * kk.y;
             }
         }
-        dot *= p.softmax_scale;
-        scores[t] = dot;
-        local_max = fmaxf(local_max, dot);
+#pragma unroll
+        for (int o = kLanesPerPos / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (t < length) {
+            dot *= p.softmax_scale;
+            if (sub == 0) scores[t] = dot;
+            local_max = fmaxf(local_max, dot);
+        }
     }
-    const float top = block_max(local_max, scratch);
+    const float top = block_max(local_max, scratch);  // its barriers also publish the scores
     float local_sum = 0.0f;
     for (int t = threadIdx.x; t < length; t += blockDim.x) {
         const float e = expf(scores[t] - top);
         scores[t] = e;
         local_sum += e;
     }
-    const float denom = block_sum(local_sum, scratch);   // also makes every score visible
-    // values: thread = (quarter of the positions, pair of dims when d == 64; single dim pair loop otherwise)
-    const int pairs = half_d;                              // half2 columns
-    const int groups = blockDim.x / pairs > 0 ? blockDim.x / pairs : 1;
-    const int group = threadIdx.x / pairs;
-    const int pair = threadIdx.x % pairs;
-    float ax = 0.0f, ay = 0.0f;
-    if (group < groups) {
-        for (int t = group; t < length; t += groups) {
+    const float denom = block_sum(local_sum, scratch);
+
+    float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+    for (int base = 0; base < length; base += kPosPerPass) {
+        const int t = base + slot;
+        if (t < length) {
             const float w = scores[t];
-            float2 vv;
-            if (t == length - 1) vv = make_float2(__half2float(v_new[2 * pair]), __half2float(v_new[2 * pair + 1]));
-            else vv = __half22float2(reinterpret_cast<const __half2*>(v_base + static_cast<size_t>(t) * d)[pair]);
-            ax += w * vv.x;
-            ay += w * vv.y;
+            const uint4 piece = row_piece(v_rows, v_new, t);
+            const __half2* h = reinterpret_cast<const __half2*>(&piece);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 vv = __half22float2(h[i]);
+                acc[2 * i] += w * vv.x;
+                acc[2 * i + 1] += w * vv.y;
+            }
         }
-        partial[group * d + 2 * pair] = ax;
-        partial[group * d + 2 * pair + 1] = ay;
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) partial[slot][sub * 8 + i] = acc[i];
     __syncthreads();
-    if (threadIdx.x < d) {
+    if (threadIdx.x < D) {
         float total = 0.0f;
-        for (int g = 0; g < groups; ++g) total += partial[g * d + threadIdx.x];
-        p.out[head * d + threadIdx.x] = __float2half_rn(total / denom);
+#pragma unroll
+        for (int g = 0; g < kPosPerPass; ++g) total += partial[g][threadIdx.x];
+        p.out[head * D + threadIdx.x] = __float2half_rn(total / denom);
     }
 }
 
@@ -231,22 +253,22 @@ int launch_attention_decode(const __half* qkv, __half* k_cache, __half* v_cache,
                             float softmax_scale, unsigned* status, bool programmatic, cudaStream_t stream) {
     AttentionParams params{qkv, k_cache, v_cache, out, position, inv_freq, q_heads, kv_heads, head_dim, max_len,
                            rope_scale, softmax_scale, status};
-    const int pairs = head_dim / 2;
-    const int groups = 128 / pairs > 0 ? 128 / pairs : 1;
-    const size_t smem = (static_cast<size_t>(max_len) + head_dim + static_cast<size_t>(groups) * head_dim) * sizeof(float);
-    if (smem > 48 * 1024) {
-        static bool raised[64] = {};
+    const size_t smem = static_cast<size_t>(max_len) * sizeof(float);      // the scores; the rest is static
+    auto kernel = head_dim == 64 ? attention_decode_kernel<64> : attention_decode_kernel<128>;
+    if (smem > 32 * 1024) {
+        if (smem > 160 * 1024) return W4A16_ERR_TOO_LARGE;
+        static bool raised[64][2] = {};
         int device = 0;
         if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return W4A16_ERR_LAUNCH;
-        if (!raised[device]) {
-            if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+        const int which = head_dim == 64 ? 0 : 1;
+        if (!raised[device][which]) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess) {
                 return W4A16_ERR_LAUNCH;
             }
-            raised[device] = true;
+            raised[device][which] = true;
         }
-        if (smem > 200 * 1024) return W4A16_ERR_TOO_LARGE;
     }
-    return launch_kernel(attention_decode_kernel, dim3(q_heads), dim3(128), smem, programmatic, stream, params);
+    return launch_kernel(kernel, dim3(q_heads), dim3(128), smem, programmatic, stream, params);
 }
 
 }  // namespace w4a16
