@@ -704,6 +704,36 @@ def run_product(args) -> dict:
         os.environ["W4A16_PDL"] = "1"
         graph = capture(torch, step)   # `outs` point at this graph's outputs again
 
+    # ---- the same token with q/k/v and gate/up concatenated along N (what fuse_parallel_linears does to a
+    # model): 89 launches instead of 155 over the same packed bytes; reported beside the headline, not as it
+    fused_siblings = None
+    if world == 1 and not args.quick:
+        fused_layers = []
+        for b in range(N_BLOCKS):
+            base = b * len(BLOCK_ORDER)
+            for members in ((0, 1, 2), (3,), (4, 5), (6,)):
+                packed = torch.cat([weights[base + m][0] for m in members]).contiguous()
+                scales = torch.cat([weights[base + m][1] for m in members]).contiguous()
+                fused_layers.append((x_dev[base + members[0]], packed, scales))
+        fused_layers.append((x_dev[-1], *weights[-1]))
+        fused_outs: list = [None] * len(fused_layers)
+
+        def fused_step():
+            for i, (x, packed, scales) in enumerate(fused_layers):
+                fused_outs[i] = linear_cuda(x, packed, scales, GROUP)
+
+        fused_graph = capture(torch, fused_step)
+        for _ in range(3):
+            fused_graph.replay()
+        barrier()
+        fused_ms = time_replays(torch, fused_graph, args.steps) / args.steps
+        fused_bytes = sum(algorithmic_bytes(1, x.shape[1], packed.shape[0]) for x, packed, _ in fused_layers)
+        fused_siblings = {"launches_per_step": len(fused_layers), "ms_per_step": round(fused_ms, 5),
+                          "value": round(fused_bytes / (fused_ms * 1e-3) / 1e9, 1), "bytes_per_step": fused_bytes}
+        log(f"  q/k/v and gate/up as single launches: {fused_siblings}")
+        del fused_graph, fused_layers, fused_outs
+        torch.cuda.empty_cache()
+
     # ---- e2e: host activations in, host outputs back, every step
     y_all_host = torch.empty((sum(n for _, _, n in layers),), dtype=torch.float16).pin_memory()
     h2d = x_all_host.numel() * 2
@@ -753,6 +783,7 @@ def run_product(args) -> dict:
         "e2e": {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": round(e2e_ms, 5)},
         "gpu_launches": args.steps * len(layers),
+        "fused_siblings": fused_siblings,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "peak_kind": peak_kind, "frac_of_8tbs": round(achieved / 8000, 4),
                      "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "kernel": "linear_mma_kernel", "mean_launch_us": round(kernel_us, 3),
