@@ -1,5 +1,6 @@
 """B200-native W4A16 linear path with the reference project's Python surface."""
-from .checkpoint import load_quantized_weight_checkpoint, save_quantized_weight_checkpoint
+from .checkpoint import (load_packed_model, load_quantized_model_checkpoint, load_quantized_weight_checkpoint,
+                         save_quantized_model_checkpoint, save_quantized_weight_checkpoint)
 from .cuda import cuda_extension_available, dequantize_cuda, linear_cuda, quantize_and_pack_cuda
 from .fusion import FusedQuantizedLinear, FusedSlice, fuse_parallel_linears
 from .integration import load_packed_state_dict, replace_linear_layers
@@ -15,6 +16,9 @@ __all__ = [
     "quantize_and_pack_weights",
     "save_quantized_weight_checkpoint",
     "load_quantized_weight_checkpoint",
+    "save_quantized_model_checkpoint",
+    "load_quantized_model_checkpoint",
+    "load_packed_model",
     "replace_linear_layers",
     "load_packed_state_dict",
     "fuse_parallel_linears",

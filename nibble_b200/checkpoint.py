@@ -76,3 +76,67 @@ def load_quantized_weight_checkpoint(
     if tuple(blob.get("original_shape", ())) != shape:
         raise ValueError("checkpoint original_shape does not match its tensors")
     return packed_weights, scales, group_size
+
+
+# ----------------------------------------------------------------------------- whole models
+# The reference writes a quantised model as one ``torch.save`` dict (scripts/quantize_tinyllama.py:71-83)
+# and reads it back into an empty model (scripts/generate.py:214-257).  Same keys here, so files interchange.
+MODEL_FORMAT_NAME = "w4a16-tinyllama"
+MODEL_FORMAT_VERSION = 1
+
+
+def save_quantized_model_checkpoint(path: str | os.PathLike, model: torch.nn.Module, group_size: int = 128,
+                                    source_model: str = "") -> None:
+    """Write the state dict of a model whose linears are already ``QuantizedLinear`` (CPU tensors, the
+    reference's keys ``format``, ``version``, ``source_model``, ``group_size``, ``state_dict``).
+
+    Layers fused by ``fuse_parallel_linears`` are written under their original names, slice by slice,
+    so the file does not depend on whether fusion was applied.
+    """
+    from .fusion import FusedQuantizedLinear, FusedSlice
+
+    state = {}
+    fused_prefixes = tuple(name + "." for name, module in model.named_modules() if isinstance(module, FusedQuantizedLinear))
+    for key, tensor in model.state_dict().items():
+        if fused_prefixes and key.startswith(fused_prefixes):
+            continue
+        state[key] = tensor.detach().cpu()
+    for name, module in model.named_modules():
+        if isinstance(module, FusedSlice):
+            state[f"{name}.packed_weights"] = module.packed_weights.detach().cpu().clone()
+            state[f"{name}.scales"] = module.scales.detach().cpu().clone()
+            if module.bias is not None:
+                state[f"{name}.bias"] = module.bias.detach().cpu().clone()
+    os.makedirs(os.path.dirname(os.path.abspath(os.fspath(path))), exist_ok=True)
+    torch.save({"format": MODEL_FORMAT_NAME, "version": MODEL_FORMAT_VERSION, "source_model": source_model,
+                "group_size": int(group_size), "state_dict": state}, os.fspath(path))
+
+
+def load_quantized_model_checkpoint(path: str | os.PathLike) -> dict:
+    """Read and validate a model checkpoint; tensors stay on the CPU (errors as in the reference)."""
+    checkpoint = torch.load(os.fspath(path), map_location="cpu", weights_only=True)
+    if not isinstance(checkpoint, dict):
+        raise ValueError("checkpoint must contain a dictionary")
+    if checkpoint.get("format") != MODEL_FORMAT_NAME:
+        raise ValueError("checkpoint has an unsupported format")
+    if checkpoint.get("version") != MODEL_FORMAT_VERSION:
+        raise ValueError("checkpoint has an unsupported version")
+    if not isinstance(checkpoint.get("group_size"), int):
+        raise ValueError("checkpoint is missing group_size")
+    if not isinstance(checkpoint.get("state_dict"), dict):
+        raise ValueError("checkpoint is missing state_dict")
+    return checkpoint
+
+
+def load_packed_model(model: torch.nn.Module, path: str | os.PathLike, device: str | torch.device = "cuda",
+                      fused: bool = True) -> int:
+    """Fill ``model`` (typically built on the meta device from a config) from a model checkpoint:
+    its linears become packed modules, everything is materialised directly on ``device`` -- FP16
+    linear weights never exist -- and the packed tensors are copied in.  Returns the number of
+    linears replaced (the reference's ``load_packed_model``, scripts/generate.py:230-257, without the
+    hub download)."""
+    from .integration import load_packed_state_dict
+
+    checkpoint = load_quantized_model_checkpoint(path)
+    return load_packed_state_dict(model, checkpoint["state_dict"], group_size=checkpoint["group_size"],
+                                  device=device, fused=fused)
