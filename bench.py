@@ -436,7 +436,7 @@ def decode_bench(torch, device) -> dict:
         decode_ms = total_ms - prefill_ms
         row = {"decode_tok_s": round((new_tokens - 1) / decode_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
                "ms_per_token": round(decode_ms / (new_tokens - 1), 4), "e2e_tok_s": round(new_tokens / total_ms * 1e3, 1),
-               "mode": "cuda_graph, own decode step", "kernels_per_token": runner.launches_per_step + 3,
+               "mode": "cuda_graph, own decode step", "kernels_per_token": runner.launches_per_step + 1,
                "cache_overrun": int(runner.status.item())}
         log(f"  decode {label}: {row}")
         return row
@@ -490,6 +490,51 @@ def run_single_layer(args) -> dict:
     peak, kind = measured_peaks()
     return {"single_layer": {"K": k, "N": n, "M": m}, "launches": args.steps, "us_per_launch_eager": round(us, 2),
             "gbs": round(payload / us / 1e3, 1), "peak": peak, "peak_kind": kind, "bytes_per_launch": payload}
+
+
+def run_decode_step(args) -> dict:
+    """`--workload decode_step`: the decode runner of nibble_b200/decode.py on the TinyLlama-1.1B-shaped model
+    (random weights), `--steps` tokens after a 16-token prompt, eager launches (no graph) between
+    cudaProfilerStart/Stop so that a profiler lists every kernel of a token."""
+    import torch
+    import transformers
+
+    from nibble_b200 import _native, replace_linear_layers
+    from nibble_b200.decode import LlamaDecodeRunner
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    if args.pdl:
+        os.environ["W4A16_PDL"] = "1"
+    cfg = transformers.LlamaConfig(
+        vocab_size=32000, hidden_size=2048, intermediate_size=5632, num_hidden_layers=22,
+        num_attention_heads=32, num_key_value_heads=4, max_position_embeddings=2048, rms_norm_eps=1e-5,
+        tie_word_embeddings=False)
+    torch.manual_seed(0)
+    with torch.device(device):
+        model = transformers.AutoModelForCausalLM.from_config(cfg, dtype=torch.float16)
+    model.eval()
+    replace_linear_layers(model, group_size=GROUP)
+    runner = LlamaDecodeRunner(model, max_len=16 + args.steps + 8)
+    prompt = torch.randint(0, 32000, (16,), generator=torch.Generator().manual_seed(0)).to(device)
+    with torch.inference_mode():
+        for i in range(16):
+            runner.token.copy_(prompt[i:i + 1])
+            runner._enqueue_step()
+        torch.cuda.synchronize()
+        before = _native.core().w4a16_launch_count()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.profiler.start()
+        start.record()
+        for _ in range(args.steps):
+            runner._enqueue_step()
+        end.record()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+    ms = start.elapsed_time(end) / args.steps
+    return {"workload": "decode_step", "tokens": args.steps, "ms_per_token_eager": round(ms, 4),
+            "our_kernels_per_token": (_native.core().w4a16_launch_count() - before) // args.steps,
+            "cache_overrun": int(runner.status.item())}
 
 
 def run_tensor_parallel(args) -> dict:
@@ -878,7 +923,7 @@ def main() -> None:
     parser.add_argument("--quick", action="store_true", help="skip the per-shape tables")
     parser.add_argument("--kernel-only", action="store_true",
                         help="only the timed region (bracketed by cudaProfilerStart/Stop), for profiler runs")
-    parser.add_argument("--workload", choices=["tinyllama_decode_linears_m1", "llama70b_tp"],
+    parser.add_argument("--workload", choices=["tinyllama_decode_linears_m1", "llama70b_tp", "decode_step"],
                         default="tinyllama_decode_linears_m1")
     parser.add_argument("--batch", type=int, default=1, help="M for --workload llama70b_tp")
     parser.add_argument("--collective", choices=["p2p", "nccl"], default="p2p",
@@ -888,6 +933,8 @@ def main() -> None:
     args = parser.parse_args()
     if args.single_layer:
         result = run_single_layer(args)
+    elif args.workload == "decode_step" and args.impl == "product":
+        result = run_decode_step(args)
     elif args.workload == "llama70b_tp" and args.impl == "product":
         result = run_tensor_parallel(args)
     else:

@@ -216,6 +216,10 @@ int w4a16_linear_f16_input(const void* x, const void* packed, const void* scales
 int w4a16_add_rmsnorm_f16(const void* stream_in, const void* delta, const void* weight, void* stream_out,
                           void* normed, int64_t hidden, float eps, uint32_t flags, w4a16_stream_t stream);
 int w4a16_silu_mul_f16(const void* gate_up, void* out, int64_t intermediate, uint32_t flags, w4a16_stream_t stream);
+/* *token = index of the first maximum of `count` FP16 logits (NaNs are never chosen); when `position` is
+ * non-NULL, *position += 1: the end of a greedy decode step in one launch. */
+int w4a16_argmax_advance_f16(const void* logits, int64_t count, int64_t* token, int64_t* position,
+                             uint32_t flags, w4a16_stream_t stream);
 int w4a16_attention_decode_f16(const void* qkv, void* k_cache, void* v_cache, void* out,
                                const int64_t* position, const float* inv_freq, int32_t q_heads,
                                int32_t kv_heads, int32_t head_dim, int32_t max_len, float rope_scale,

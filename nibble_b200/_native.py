@@ -70,6 +70,7 @@ C_API = {
     "w4a16_linear_f16_input": (ctypes.c_int, [_P, _P, _P, _P, _I, _I, _I, _I, _P, ctypes.c_size_t, ctypes.c_uint32, _P, _P]),
     "w4a16_add_rmsnorm_f16": (ctypes.c_int, [_P, _P, _P, _P, _P, _I, ctypes.c_float, ctypes.c_uint32, _P]),
     "w4a16_silu_mul_f16": (ctypes.c_int, [_P, _P, _I, ctypes.c_uint32, _P]),
+    "w4a16_argmax_advance_f16": (ctypes.c_int, [_P, _I, _P, _P, ctypes.c_uint32, _P]),
     "w4a16_attention_decode_f16": (
         ctypes.c_int,
         [_P, _P, _P, _P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_float,

@@ -255,6 +255,15 @@ int w4a16_silu_mul_f16(const void* gate_up, void* out, int64_t intermediate, uin
                                   reinterpret_cast<cudaStream_t>(stream));
 }
 
+int w4a16_argmax_advance_f16(const void* logits, int64_t count, int64_t* token, int64_t* position, uint32_t flags,
+                             w4a16_stream_t stream) {
+    if (count <= 0 || count > INT32_MAX - 8192) return W4A16_ERR_BAD_SHAPE;
+    if (logits == nullptr || token == nullptr) return W4A16_ERR_NULL_POINTER;
+    return w4a16::launch_argmax_advance(static_cast<const __half*>(logits), static_cast<int>(count),
+                                        reinterpret_cast<long long*>(token), reinterpret_cast<long long*>(position),
+                                        (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0, reinterpret_cast<cudaStream_t>(stream));
+}
+
 int w4a16_attention_decode_f16(const void* qkv, void* k_cache, void* v_cache, void* out, const int64_t* position,
                                const float* inv_freq, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_len,
                                float rope_scale, float softmax_scale, uint32_t* status, uint32_t flags,

@@ -84,6 +84,54 @@ silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ out, in
     out[i] = __hmul(act, gate_up[inter + i]);
 }
 
+// token = index of the first largest logit (what argmax returns); the position moves on by one.
+__global__ void __launch_bounds__(1024)
+argmax_advance_kernel(const __half* __restrict__ logits, int count, long long* __restrict__ token,
+                      long long* __restrict__ position) {
+    __shared__ float best_value[32];
+    __shared__ int best_index[32];
+    pdl_release_downstream();
+    pdl_wait_for_upstream();
+    float value = -INFINITY;
+    int index = 0x7fffffff;
+    for (int i = threadIdx.x * 8; i < count; i += blockDim.x * 8) {
+        if (i + 8 <= count && (reinterpret_cast<uintptr_t>(logits + i) & 15) == 0) {
+            const uint4 q = *reinterpret_cast<const uint4*>(logits + i);
+            const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                if (f.x > value) { value = f.x; index = i + 2 * j; }
+                if (f.y > value) { value = f.y; index = i + 2 * j + 1; }
+            }
+        } else {
+            for (int j = i; j < min(i + 8, count); ++j) {
+                const float f = __half2float(logits[j]);
+                if (f > value) { value = f; index = j; }
+            }
+        }
+    }
+    auto merge = [&](float other_value, int other_index) {
+        if (other_value > value || (other_value == value && other_index < index)) { value = other_value; index = other_index; }
+    };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) merge(__shfl_xor_sync(0xffffffffu, value, o), __shfl_xor_sync(0xffffffffu, index, o));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { best_value[warp] = value; best_index[warp] = index; }
+    __syncthreads();
+    if (warp == 0) {
+        const int warps = blockDim.x >> 5;
+        value = lane < warps ? best_value[lane] : -INFINITY;
+        index = lane < warps ? best_index[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) merge(__shfl_xor_sync(0xffffffffu, value, o), __shfl_xor_sync(0xffffffffu, index, o));
+        if (lane == 0) {
+            *token = index == 0x7fffffff ? 0 : index;
+            if (position != nullptr) *position += 1;
+        }
+    }
+}
+
 struct AttentionParams {
     const __half* qkv;        // [q heads * d | kv heads * d | kv heads * d] of this token
     __half* k_cache;          // [kv heads][max_len][d]
@@ -111,12 +159,29 @@ attention_decode_kernel(const AttentionParams p) {
     __shared__ __align__(16) __half k_new[D];
     __shared__ __align__(16) __half v_new[D];
     __shared__ float partial[kPosPerPass][D];
+    constexpr int kEarlyPasses = 2;                   // passes whose cache rows are requested before anything else
     const int head = blockIdx.x;
     constexpr int half_d = D / 2;
     const int kv_head = head / (p.q_heads / p.kv_heads);
+    const int sub = threadIdx.x % kLanesPerPos;       // which 8 of the D dims
+    const int slot = threadIdx.x / kLanesPerPos;      // which position of a pass
+    const uint4* k_rows = reinterpret_cast<const uint4*>(p.k_cache + static_cast<size_t>(kv_head) * p.max_len * D) + sub;
+    const uint4* v_rows = reinterpret_cast<const uint4*>(p.v_cache + static_cast<size_t>(kv_head) * p.max_len * D) + sub;
     pdl_release_downstream();
-    pdl_wait_for_upstream();
+    // Nothing below depends on the kernel just before this one (it produces qkv): the position was set
+    // and the older cache rows were written by earlier steps.  So the first rows of K and V, the position
+    // and the rotary frequencies are requested before waiting for that kernel.  Rows at or past the
+    // position hold stale data; they are fetched (inside the cache) and never used.
+    uint4 k_early[kEarlyPasses], v_early[kEarlyPasses];
+#pragma unroll
+    for (int e = 0; e < kEarlyPasses; ++e) {
+        const int t = min(e * kPosPerPass + slot, p.max_len - 1);
+        k_early[e] = k_rows[static_cast<size_t>(t) * kLanesPerPos];
+        v_early[e] = v_rows[static_cast<size_t>(t) * kLanesPerPos];
+    }
     const long long pos = *p.position;
+    const float freq = p.inv_freq[threadIdx.x % half_d];
+    pdl_wait_for_upstream();
     if (pos < 0 || pos >= p.max_len) {
         if (threadIdx.x == 0) atomicMax(p.status, 1u);
         return;
@@ -127,8 +192,7 @@ attention_decode_kernel(const AttentionParams p) {
     // rotary embedding, rounded as the framework rounds it: cos/sin to FP16, two FP16 products, one FP16 sum
     if (threadIdx.x < D) {
         const int i = threadIdx.x;
-        const int f = i < half_d ? i : i - half_d;
-        const float angle = static_cast<float>(pos) * p.inv_freq[f];
+        const float angle = static_cast<float>(pos) * freq;
         float sn, cs;
         sincosf(angle, &sn, &cs);
         const __half c = __float2half_rn(cs * p.rope_scale);
@@ -148,13 +212,12 @@ attention_decode_kernel(const AttentionParams p) {
     __syncthreads();
 
     const int length = static_cast<int>(pos) + 1;
-    const int sub = threadIdx.x % kLanesPerPos;       // which 8 of the D dims
-    const int slot = threadIdx.x / kLanesPerPos;      // which position of a pass
-    const uint4* k_rows = reinterpret_cast<const uint4*>(p.k_cache + static_cast<size_t>(kv_head) * p.max_len * D) + sub;
-    const uint4* v_rows = reinterpret_cast<const uint4*>(p.v_cache + static_cast<size_t>(kv_head) * p.max_len * D) + sub;
     // The newest position comes from shared memory, not from the cache: another CTA writes it there.
-    auto row_piece = [&](const uint4* rows, const __half* newest, int t) {
-        return t == length - 1 ? reinterpret_cast<const uint4*>(newest)[sub] : rows[static_cast<size_t>(t) * kLanesPerPos];
+    auto row_piece = [&](const uint4* rows, const __half* newest, const uint4 (&early)[kEarlyPasses], int base, int t) {
+        if (t == length - 1) return reinterpret_cast<const uint4*>(newest)[sub];
+        if (base == 0) return early[0];
+        if (base == kPosPerPass) return early[1];
+        return rows[static_cast<size_t>(t) * kLanesPerPos];
     };
     float qf[8];
 #pragma unroll
@@ -166,7 +229,7 @@ attention_decode_kernel(const AttentionParams p) {
         const int t = base + slot;
         float dot = 0.0f;
         if (t < length) {
-            const uint4 piece = row_piece(k_rows, k_new, t);
+            const uint4 piece = row_piece(k_rows, k_new, k_early, base, t);
             const __half2* h = reinterpret_cast<const __half2*>(&piece);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -197,7 +260,7 @@ attention_decode_kernel(const AttentionParams p) {
         const int t = base + slot;
         if (t < length) {
             const float w = scores[t];
-            const uint4 piece = row_piece(v_rows, v_new, t);
+            const uint4 piece = row_piece(v_rows, v_new, v_early, base, t);
             const __half2* h = reinterpret_cast<const __half2*>(&piece);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -246,6 +309,11 @@ int launch_add_rmsnorm(const __half* stream_in, const __half* delta, const __hal
 
 int launch_silu_mul(const __half* gate_up, __half* out, int inter, bool programmatic, cudaStream_t stream) {
     return launch_kernel(silu_mul_kernel, dim3((inter + 255) / 256), dim3(256), 0, programmatic, stream, gate_up, out, inter);
+}
+
+int launch_argmax_advance(const __half* logits, int count, long long* token, long long* position, bool programmatic,
+                          cudaStream_t stream) {
+    return launch_kernel(argmax_advance_kernel, dim3(1), dim3(1024), 0, programmatic, stream, logits, count, token, position);
 }
 
 int launch_attention_decode(const __half* qkv, __half* k_cache, __half* v_cache, __half* out, const long long* position,

@@ -65,6 +65,8 @@ int launch_dequantize(const uint8_t* packed, const __half* scales, __half* weigh
 // Kernels either side of the linears in a LLaMA decode step (decode_ops.cu).
 int launch_add_rmsnorm(const __half* stream_in, const __half* delta, const __half* weight, __half* stream_out,
                        __half* normed, int hidden, float eps, bool programmatic, cudaStream_t stream);
+int launch_argmax_advance(const __half* logits, int count, long long* token, long long* position, bool programmatic,
+                          cudaStream_t stream);
 int launch_silu_mul(const __half* gate_up, __half* out, int inter, bool programmatic, cudaStream_t stream);
 int launch_attention_decode(const __half* qkv, __half* k_cache, __half* v_cache, __half* out, const long long* position,
                             const float* inv_freq, int q_heads, int kv_heads, int head_dim, int max_len, float rope_scale,

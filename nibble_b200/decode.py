@@ -1,7 +1,7 @@
 """Batch-1 decode runner for LLaMA-architecture models whose linears are ``QuantizedLinear``.
 
 Replaces, for the decode step, what the reference gets from HuggingFace ``model.generate`` with a
-static cache (scripts/generate.py:260-365): one token is ``1 + 8 * layers + 3`` kernel launches --
+static cache (scripts/generate.py:260-365): one token is ``8 * layers + 4`` kernel launches without input fusion, ``5 * layers + 3`` with it --
 per block four W4A16 linears (q/k/v fused, o, gate/up fused, down) and one attention kernel that also
 applies RoPE and appends to the cache; the two add+RMSNorm and the SiLU*up of a block are computed
 inside the linears that consume them, while those stage their activations (``fuse_inputs``; without
@@ -77,6 +77,13 @@ def linear_with_input(layer: QuantizedLinear, x: torch.Tensor, out: torch.Tensor
         layer.group_size, _ptr(workspace), workspace.numel(), _flags(),
         None if transform is None else ctypes.byref(transform),
         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "linear_with_input")
+
+
+def argmax_advance(logits: torch.Tensor, token: torch.Tensor, position: torch.Tensor | None) -> None:
+    """``token[0] = argmax(logits)`` (first maximum) and ``position[0] += 1`` in one launch."""
+    lib = _native.core()
+    _check(lib.w4a16_argmax_advance_f16(_ptr(logits), logits.numel(), _ptr(token), _ptr(position), _flags(),
+                                        ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "argmax_advance")
 
 
 def _owner_of(parent: torch.nn.Module, names: tuple[str, ...]) -> QuantizedLinear:
@@ -182,8 +189,7 @@ class LlamaDecodeRunner:
             linear_with_input(layer["down"], self.gate_up_out, self.down_out, ws, silu)
             delta = self.down_out
         linear_with_input(self.lm_head, a, self.logits, ws, self._norm_into(a, delta, self.final_norm, None))
-        torch.argmax(self.logits, dim=-1, out=self.token)
-        self.position.add_(1)
+        argmax_advance(self.logits, self.token, self.position)
 
     def _enqueue_step(self) -> None:
         if self.fuse_inputs:
@@ -203,8 +209,7 @@ class LlamaDecodeRunner:
             delta = layer["down"](self.act)
         add_rmsnorm(self.stream, delta, self.final_norm, self.eps, self.normed)
         self.logits = self.lm_head(self.normed)
-        torch.argmax(self.logits, dim=-1, out=self.token)
-        self.position.add_(1)
+        argmax_advance(self.logits, self.token, self.position)
 
     def step(self) -> None:
         """Consumes ``self.token`` at ``self.position``; leaves the greedy next token in ``self.token``."""

@@ -92,6 +92,24 @@ def test_attention_decode_matches_rope_plus_sdpa(q_heads, kv_heads, head_dim):
     assert status.item() == 1
 
 
+def test_argmax_advance_picks_the_first_maximum():
+    from nibble_b200.decode import argmax_advance
+
+    g = torch.Generator().manual_seed(3)
+    token = torch.zeros((1,), dtype=torch.long, device="cuda")
+    position = torch.full((1,), 41, dtype=torch.long, device="cuda")
+    for count in (1, 7, 512, 32000, 32003):
+        logits = torch.randn((1, count), generator=g).half().cuda()
+        argmax_advance(logits, token, position)
+        assert token.item() == int(torch.argmax(logits.float()).item())
+    assert position.item() == 46
+    logits = torch.zeros((1, 32000), dtype=torch.float16, device="cuda")
+    logits[0, 12345] = 3.0
+    logits[0, 777] = 3.0                     # a tie: the lower index, as torch.argmax gives
+    argmax_advance(logits, token, None)
+    assert token.item() == 777 and position.item() == 46
+
+
 def test_linear_with_fused_input_equals_the_separate_kernels():
     import ctypes
 
@@ -166,7 +184,7 @@ def test_runner_logits_follow_the_framework_forward():
             out = model(input_ids=tokens[t].view(1, 1), past_key_values=cache,
                         cache_position=torch.tensor([t], device="cuda"), use_cache=True)
             want.append(out.logits[0, -1].float().clone())
-    for fuse_inputs, per_block, tail in ((False, 8, 2), (True, 5, 1)):
+    for fuse_inputs, per_block, tail in ((False, 8, 3), (True, 5, 2)):
         runner = LlamaDecodeRunner(model, max_len=32, fuse_inputs=fuse_inputs)
         assert runner.launches_per_step == 0
         worst = 0.0
