@@ -10,7 +10,9 @@ replayed with the token and the position living in device memory.
 
 The arithmetic follows transformers' LlamaDecoderLayer rounding by rounding (FP16 residual sums,
 FP32 RMSNorm statistics, FP16 rotary products, FP32 softmax), so logits agree with the framework's
-eager forward up to summation order.  Prompts are consumed one token per step (no batched prefill).
+eager forward up to summation order.  Short prompts are consumed one token per step; longer ones go
+through the model's own batched forward once (its linears then run the prefill kernels) and the
+resulting keys and values are copied into the runner's caches, which use the same layout.
 """
 from __future__ import annotations
 
@@ -109,6 +111,7 @@ class LlamaDecodeRunner:
 
     def __init__(self, model: torch.nn.Module, max_len: int, fuse_inputs: bool | None = None):
         config = model.config
+        self.model = model
         self.hidden = config.hidden_size
         self.q_heads = config.num_attention_heads
         self.kv_heads = config.num_key_value_heads
@@ -234,16 +237,43 @@ class LlamaDecodeRunner:
         self.position.zero_()
         self.status.zero_()
 
-    def generate(self, prompt_ids: torch.Tensor, new_tokens: int) -> torch.Tensor:
+    # Prompts up to this many tokens are cheaper one decode step at a time than through the framework's
+    # batched forward (about half a millisecond per token against a fixed ~12 ms).
+    STEPPED_PREFILL_MAX = 24
+
+    def prefill(self, prompt_ids: torch.Tensor, batched: bool | None = None) -> None:
+        """Consume a 1-D prompt from position 0; leaves the first generated token in ``self.token``."""
+        prompt = prompt_ids.reshape(-1).to(self.token.device)
+        if prompt.numel() == 0 or prompt.numel() >= self.max_len:
+            raise ValueError("the prompt must hold at least one token and fit the cache")
+        self.reset()
+        if batched is None:
+            batched = prompt.numel() > self.STEPPED_PREFILL_MAX
+        if not batched:
+            for i in range(prompt.numel()):
+                self.token.copy_(prompt[i:i + 1])
+                self.step()
+            return
+        from transformers import StaticCache
+
+        count = prompt.numel()
+        with torch.inference_mode():
+            cache = StaticCache(config=self.model.config, max_cache_len=self.max_len)
+            out = self.model(input_ids=prompt.view(1, -1), past_key_values=cache,
+                             cache_position=torch.arange(count, device=prompt.device), use_cache=True)
+            for index, layer in enumerate(cache.layers):
+                self.k_cache[index, :, :count].copy_(layer.keys[0, :, :count])
+                self.v_cache[index, :, :count].copy_(layer.values[0, :, :count])
+            self.token.copy_(out.logits[0, -1:].argmax(-1))
+            self.position.fill_(count)
+
+    def generate(self, prompt_ids: torch.Tensor, new_tokens: int, batched_prefill: bool | None = None) -> torch.Tensor:
         """Greedy continuation of a 1-D prompt; returns the ``new_tokens`` generated ids."""
         prompt = prompt_ids.reshape(-1).to(self.token.device)
         if prompt.numel() + new_tokens > self.max_len:
             raise ValueError("prompt + new tokens exceed the cache length")
-        self.reset()
         out = torch.empty((new_tokens,), dtype=torch.long, device=self.token.device)
-        for i in range(prompt.numel()):
-            self.token.copy_(prompt[i:i + 1])
-            self.step()
+        self.prefill(prompt, batched_prefill)
         for i in range(new_tokens):
             out[i:i + 1].copy_(self.token)
             if i + 1 < new_tokens:

@@ -217,3 +217,30 @@ def test_generate_is_repeatable_and_checks_the_cache_length():
     assert first.shape == (12,) and torch.equal(first, second)
     with pytest.raises(ValueError):
         runner.generate(prompt, 21)
+
+
+def test_batched_prefill_through_the_model_lands_in_the_runners_cache():
+    from nibble_b200 import replace_linear_layers
+    from nibble_b200.decode import LlamaDecodeRunner
+
+    cfg = _config(num_hidden_layers=2)
+    torch.manual_seed(5)
+    with torch.device("cuda"):
+        model = transformers.AutoModelForCausalLM.from_config(cfg, dtype=torch.float16)
+    model.eval()
+    replace_linear_layers(model, group_size=128)
+    runner = LlamaDecodeRunner(model, max_len=96)
+    prompt = torch.randint(0, cfg.vocab_size, (70,), generator=torch.Generator().manual_seed(6))
+    runner.prefill(prompt, batched=False)
+    k_stepped, v_stepped = runner.k_cache[:, :, :70].clone(), runner.v_cache[:, :, :70].clone()
+    runner.step()
+    logits_stepped = runner.logits.float().clone()
+    runner.prefill(prompt)                         # 70 tokens: the batched route by default
+    assert int(runner.position.item()) == 70
+    torch.testing.assert_close(runner.k_cache[:, :, :70], k_stepped, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(runner.v_cache[:, :, :70], v_stepped, rtol=3e-2, atol=3e-2)
+    runner.step()
+    scale = logits_stepped.abs().max().item()
+    assert (runner.logits.float() - logits_stepped).abs().max().item() / scale < 3e-2
+    out = runner.generate(prompt, 8)
+    assert out.shape == (8,) and int(runner.position.item()) == 70 + 7
