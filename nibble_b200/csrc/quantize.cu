@@ -6,10 +6,11 @@
 //   scale = half(step)                                     (rounded after the codes are made)
 // byte j of a row holds code 2j in its low nibble and code 2j+1 in its high nibble.
 //
-// One warp per group.  A lane takes four consecutive weights per pass (one 8- or 16-byte load, one
-// 2-byte store), so a 128-wide group is one pass; the group maximum is a shuffle reduction.  The
-// weights are read twice (maximum, then codes); the second read hits L1/L2.  Bound: HBM, 2.5 (FP16
-// input) or 4.5 (FP32) bytes per weight.
+// 128-wide groups (the format's default): half a warp per group, a lane keeps its eight consecutive
+// weights in registers (one 16-byte load for FP16, two for FP32), the group maximum is a four-step
+// shuffle reduction inside the half warp, and the eight codes leave as one 4-byte store.  Bound: HBM,
+// 2.5 (FP16 input) or 4.5 (FP32) bytes per weight; the IEEE divisions keep it near the issue limit.
+// Other group sizes: one warp per group, weights read twice (maximum, then codes).
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -65,9 +66,62 @@ quantize_pack_kernel(const T* __restrict__ weights, uint8_t* __restrict__ packed
     }
 }
 
+__device__ __forceinline__ void load8(const __half* p, float (&w)[8]) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        w[2 * i] = f.x;
+        w[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void load8(const float* p, float (&w)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0];
+    const float4 b = reinterpret_cast<const float4*>(p)[1];
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+    w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+}
+
+// group == 128 and 16-byte aligned weights: sixteen lanes per group, eight weights per lane
+template <typename T>
+__global__ void __launch_bounds__(256)
+quantize_pack_128_kernel(const T* __restrict__ weights, uint8_t* __restrict__ packed, __half* __restrict__ scales,
+                         int64_t total_groups) {
+    const int lane16 = threadIdx.x & 15;
+    const int64_t halves = static_cast<int64_t>(gridDim.x) * (blockDim.x >> 4);
+    // every lane of a warp runs the same number of rounds: the shuffles below name the whole warp
+    const int64_t rounds = (total_groups + halves - 1) / halves;
+    int64_t g = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 4) + (threadIdx.x >> 4);
+    for (int64_t r = 0; r < rounds; ++r, g += halves) {
+        const bool live = g < total_groups;
+        float w[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        if (live) load8(weights + g * 128 + lane16 * 8, w);
+        float amax = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(w[i]));
+#pragma unroll
+        for (int offset = 8; offset > 0; offset >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+        if (!live) continue;
+        const float step = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 7.0f);
+        unsigned word = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) word |= code_of(w[i], step) << (4 * i);
+        reinterpret_cast<uint32_t*>(packed + g * 64)[lane16] = word;
+        if (lane16 == 0) scales[g] = __float2half_rn(step);
+    }
+}
+
 template <typename T>
 int launch(const T* weights, uint8_t* packed, __half* scales, int64_t N, int64_t K, int64_t group, cudaStream_t stream) {
     const int64_t total_groups = N * (K / group);
+    if (group == 128 && reinterpret_cast<uintptr_t>(weights) % 16 == 0 && reinterpret_cast<uintptr_t>(packed) % 4 == 0) {
+        const int64_t fast_blocks = std::min<int64_t>((total_groups + 15) / 16, 148 * 32);
+        quantize_pack_128_kernel<T><<<static_cast<unsigned>(fast_blocks), 256, 0, stream>>>(weights, packed, scales, total_groups);
+        if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
+        g_launch_count.fetch_add(1, std::memory_order_relaxed);
+        return W4A16_OK;
+    }
     const int64_t blocks = std::min<int64_t>((total_groups + 7) / 8, 148 * 64);
     quantize_pack_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(weights, packed, scales, total_groups,
                                                                               static_cast<int>(group));
