@@ -266,6 +266,40 @@ def prefill_table(torch, device) -> dict:
     return out
 
 
+def quantize_table(torch, device) -> dict:
+    """Device quantise+pack and dequantise of one Llama-70B gate/up matrix (28672 x 8192): microseconds and
+    algorithmic GB/s (2.5 bytes per weight with FP16 weights), median of 7 timings of 3 calls."""
+    from nibble_b200 import dequantize_cuda, quantize_and_pack_cuda
+
+    k, n = LLAMA70B["gate_up_proj"]
+    weights = (torch.randn((n, k), device=device) * 0.02).half()
+    packed, scales = quantize_and_pack_cuda(weights, GROUP)
+
+    def timed(fn) -> float:
+        fn()
+        samples = []
+        for _ in range(7):
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            for _ in range(3):
+                fn()
+            end.record()
+            torch.cuda.synchronize()
+            samples.append(start.elapsed_time(end) * 1000.0 / 3)
+        return statistics.median(samples)
+
+    payload = n * k * 2.5 + n * (k // GROUP) * 2
+    peak, _ = measured_peaks()
+    out = {}
+    for name, fn in (("quantize_pack_f16", lambda: quantize_and_pack_cuda(weights, GROUP)),
+                     ("dequantize_f16", lambda: dequantize_cuda(packed, scales, GROUP))):
+        us = timed(fn)
+        out[name] = {"us": round(us, 1), "gbs": round(payload / us / 1e3, 1), "frac_measured": round(payload / us / 1e3 / peak, 3)}
+    log(f"  quantise / dequantise 28672 x 8192: {out}")
+    return out
+
+
 def cpu_pass(torch, layers, sample_name: str, repeats: int) -> dict:
     """Times the CPU restatement on `layers` (list of (name, K, N)); returns GB/s over the sample."""
     from nibble_b200 import quantize_and_pack_weights
@@ -851,6 +885,7 @@ def run_product(args) -> dict:
         }
         log("prefill-sized batches (tcgen05 kernel)")
         result["prefill"] = prefill_table(torch, device)
+        result["quantize"] = quantize_table(torch, device)
     if rank == 0 and world == 1 and not args.quick:
         log("decode tokens/s, TinyLlama-1.1B-shaped model")
         try:
