@@ -1,8 +1,8 @@
 // packed INT4 + FP16 scales -> FP16 [N, K], bit-identical to half(float(code) * float(scale)).
 // Replaces the reference's int4_dequantize_kernel (csrc/int4_linear_kernel.cu:419-451).
 //
-// Pure streaming: N*K/2 bytes in, 2*N*K bytes out.  A thread owns one 32-bit word (8 codes) and
-// writes one 16-byte vector, so a warp reads 128 contiguous bytes and writes 512 contiguous bytes;
+// Pure streaming: N*K/2 bytes in, 2*N*K bytes out.  A thread owns one 32-bit word (8 codes) at a time
+// and writes one 16-byte vector, so a warp reads 128 contiguous bytes and writes 512 contiguous bytes;
 // the grid is a multiple of the SM count and strides over the matrix.
 // code * scale in a single FP16 multiply rounds once from the exact product, which is what
 // rounding the FP32 product to FP16 does (|code| <= 8 needs 4 bits, an FP16 significand 11).
@@ -22,25 +22,35 @@ __global__ void __launch_bounds__(kDequantThreads)
 dequantize_kernel(const uint32_t* __restrict__ packed_words, const __half* __restrict__ scales,
                   uint4* __restrict__ out, int64_t total_words, int words_per_row, int words_per_group,
                   int groups_per_row) {
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * kDequantThreads;
-    int64_t base = static_cast<int64_t>(blockIdx.x) * kDequantThreads + threadIdx.x;
-    for (; base < total_words; base += stride * kWordsPerThread) {
+    // A warp owns 128 consecutive words per round: lane l takes words l, l+32, l+64, l+96 of them, so
+    // every load instruction reads 128 contiguous bytes and every store writes 512.  Row and column
+    // are divided out once per round and walked forward for the other three words.
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (kDequantThreads / 32);
+    const int64_t first_warp = static_cast<int64_t>(blockIdx.x) * (kDequantThreads / 32) + (threadIdx.x >> 5);
+    for (int64_t chunk = first_warp * 128; chunk < total_words; chunk += warps * 128) {
         uint32_t word[kWordsPerThread];
         uint32_t scale2[kWordsPerThread];
+        const int64_t w0 = chunk + lane;
+        int64_t row = w0 / words_per_row;
+        int col = static_cast<int>(w0 - row * words_per_row);
 #pragma unroll
         for (int i = 0; i < kWordsPerThread; ++i) {
-            const int64_t w = base + i * stride;
+            const int64_t w = w0 + i * 32;
             if (w < total_words) {
                 word[i] = ldg_stream4(packed_words + w);
-                const int64_t row = w / words_per_row;
-                const int col = static_cast<int>(w - row * words_per_row);
                 const uint32_t s = ldg_nc_u16(scales + row * groups_per_row + col / words_per_group);
                 scale2[i] = s | (s << 16);
+            }
+            col += 32;
+            while (col >= words_per_row) {
+                col -= words_per_row;
+                ++row;
             }
         }
 #pragma unroll
         for (int i = 0; i < kWordsPerThread; ++i) {
-            const int64_t w = base + i * stride;
+            const int64_t w = w0 + i * 32;
             if (w < total_words) {
                 uint32_t h[4];
                 unpack8(word[i], h);   // (c0,c4) (c1,c5) (c2,c6) (c3,c7)
