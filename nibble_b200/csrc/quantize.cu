@@ -32,6 +32,18 @@ __device__ __forceinline__ unsigned code_of(float w, float step) {
     return static_cast<unsigned>(static_cast<int>(q)) & 0xFu;
 }
 
+// Same code as code_of, without the IEEE division for all but a sliver of inputs: q = w * (1/step) is
+// within a few ulp of w / step, so whenever q is not within 1e-4 of a rounding tie (k + 0.5) both the true
+// quotient and its FP32 rounding lie strictly inside the same rounding interval and rint(q) is the
+// reference's answer; the rare near-tie input takes the exact route.
+__device__ __forceinline__ unsigned code_near(float w, float step, float inv_step) {
+    const float q = w * inv_step;
+    float r = rintf(q);
+    if (fabsf(q - r) > 0.4999f) r = rintf(__fdiv_rn(w, step));
+    r = fminf(fmaxf(r, -7.0f), 7.0f);
+    return static_cast<unsigned>(static_cast<int>(r)) & 0xFu;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 quantize_pack_kernel(const T* __restrict__ weights, uint8_t* __restrict__ packed, __half* __restrict__ scales,
@@ -104,9 +116,10 @@ quantize_pack_128_kernel(const T* __restrict__ weights, uint8_t* __restrict__ pa
         for (int offset = 8; offset > 0; offset >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
         if (!live) continue;
         const float step = amax == 0.0f ? 1.0f : __fdiv_rn(amax, 7.0f);
+        const float inv_step = __fdiv_rn(1.0f, step);
         unsigned word = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) word |= code_of(w[i], step) << (4 * i);
+        for (int i = 0; i < 8; ++i) word |= code_near(w[i], step, inv_step) << (4 * i);
         reinterpret_cast<uint32_t*>(packed + g * 64)[lane16] = word;
         if (lane16 == 0) scales[g] = __float2half_rn(step);
     }

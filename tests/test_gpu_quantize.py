@@ -74,3 +74,23 @@ def test_c_abi_validation():
     assert lib.w4a16_quantize_pack_f16(None, p.data_ptr(), s.data_ptr(), 4, 128, 128, stream) == -1
     assert lib.w4a16_quantize_pack_f32(w.data_ptr(), p.data_ptr(), s.data_ptr(), 0, 128, 128, stream) == 0
     torch.cuda.synchronize()
+
+
+def test_near_tie_quotients_match_the_host_division():
+    # weights placed within a few ulp of every rounding tie k + 0.5 of w / step, for awkward steps
+    g = torch.Generator().manual_seed(21)
+    rows = []
+    for _ in range(64):
+        amax = float(torch.rand((), generator=g) * 3 + 0.01)
+        step = torch.tensor(amax, dtype=torch.float32) / 7.0
+        ties = (torch.arange(-7, 7, dtype=torch.float32) + 0.5) * step
+        near = torch.cat([ties, torch.nextafter(ties, torch.tensor(10.0)), torch.nextafter(ties, torch.tensor(-10.0)),
+                          ties * (1 + 3e-7), ties * (1 - 3e-7)])
+        row = torch.zeros(128)
+        row[: near.numel()] = near
+        row[-1] = amax
+        rows.append(row)
+    w = torch.stack(rows)
+    packed, scales = quantize_and_pack_cuda(w.cuda(), 128)
+    want_packed, want_scales = _host(w, 128)
+    assert torch.equal(packed.cpu(), want_packed) and torch.equal(scales.cpu(), want_scales)
