@@ -879,6 +879,8 @@ def run_product(args) -> dict:
         log("per-shape latency, rotating weight copies (TinyLlama shapes)")
         result["layers"] = {
             "tinyllama_m1": per_shape_table(torch, TINYLLAMA, 1, device, l2, with_cublas=True),
+            "tinyllama_m2": per_shape_table(torch, TINYLLAMA, 2, device, l2, with_cublas=True),
+            "tinyllama_m4": per_shape_table(torch, TINYLLAMA, 4, device, l2, with_cublas=True),
             "tinyllama_m8": per_shape_table(torch, TINYLLAMA, 8, device, l2, with_cublas=True),
             "llama70b_m1": per_shape_table(torch, LLAMA70B, 1, device, l2, with_cublas=False),
             "llama70b_m8": per_shape_table(torch, LLAMA70B, 8, device, l2, with_cublas=True),
