@@ -79,9 +79,8 @@ silu_mul_kernel(const __half* __restrict__ gate_up, __half* __restrict__ out, in
     pdl_wait_for_upstream();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= inter) return;
-    const float g = __half2float(gate_up[i]);
-    const __half act = __float2half_rn(g / (1.0f + expf(-g)));
-    out[i] = __hmul(act, gate_up[inter + i]);
+    const __half2 act = silu_half2(__half2half2(gate_up[i]));
+    out[i] = __hmul(__low2half(act), gate_up[inter + i]);
 }
 
 // token = index of the first largest logit (what argmax returns); the position moves on by one.

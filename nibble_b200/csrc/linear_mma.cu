@@ -108,11 +108,7 @@ __device__ __forceinline__ uint4 silu_mul8(const uint4& gate, const uint4& up) {
     const Half8 g = as_half8(gate), u = as_half8(up);
     Half8 out;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = __half22float2(g.v[i]);
-        const __half2 act = __floats2half2_rn(f.x / (1.0f + expf(-f.x)), f.y / (1.0f + expf(-f.y)));
-        out.v[i] = __hmul2(act, u.v[i]);
-    }
+    for (int i = 0; i < 4; ++i) out.v[i] = __hmul2(silu_half2(g.v[i]), u.v[i]);
     return as_uint4(out);
 }
 

@@ -116,6 +116,13 @@ __device__ __forceinline__ void mma_m16n8k16_from(float (&d)[4], const float (&c
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
 
+// half(silu(g)) for a pair: FP32 with the fast exponential and division (a few ulp of FP32, far below
+// the FP16 rounding that follows), then one rounding to FP16 -- where a framework rounds silu's result.
+__device__ __forceinline__ __half2 silu_half2(__half2 gate) {
+    const float2 f = __half22float2(gate);
+    return __floats2half2_rn(__fdividef(f.x, 1.0f + __expf(-f.x)), __fdividef(f.y, 1.0f + __expf(-f.y)));
+}
+
 // Programmatic dependent launch.  Both are no-ops for a kernel launched the ordinary way.
 __device__ __forceinline__ void pdl_wait_for_upstream() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
