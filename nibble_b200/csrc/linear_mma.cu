@@ -338,8 +338,7 @@ linear_mma_kernel(const MmaParams p) {
 
     // ---- stage this CTA's slice of x in shared memory, in B-fragment order --------------------
     // 16-byte unit ((c * 4 + i) * XB + n) * 4 + t holds, for batch row n, the eight activations
-    // k = c*128 + t*32 + i*8 .. +8 re-paired as (x0,x4)(x1,x5)(x2,x6)(x3,x7).  Rows past the batch
-    // repeat its last row: their products land in output columns that are never stored.
+    // k = c*128 + t*32 + i*8 .. +8 re-paired as (x0,x4)(x1,x5)(x2,x6)(x3,x7).
     // With p.x_mode set, the activations are computed here from what produced them: silu(gate) * up of
     // a fused gate/up output, or the RMSNorm of the residual stream plus the last block's output (one
     // CTA also writes the summed stream back).
@@ -401,8 +400,12 @@ linear_mma_kernel(const MmaParams p) {
                 put(as_uint4(x8), j, 0);
             }
         } else {
-            for (int n = 0; n < XB; ++n) {
-                const int src_row = m0 + min(n, batch_here - 1);
+            // Only the rows that exist are staged.  The B-fragment columns of the rows past the batch then hold
+            // whatever the shared memory held; each output column depends on its own activation row alone and
+            // those columns are never stored.
+            const int staged_rows = XB == 1 ? 1 : batch_here;
+            for (int n = 0; n < staged_rows; ++n) {
+                const int src_row = m0 + n;
                 const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(src_row) * p.x_ld +
                                                                   static_cast<size_t>(c_begin) * kGroup);
                 if (p.x_mode == W4A16_INPUT_SILU_MUL) {
