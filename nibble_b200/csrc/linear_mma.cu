@@ -404,15 +404,48 @@ linear_mma_kernel(const MmaParams p) {
             // whatever the shared memory held; each output column depends on its own activation row alone and
             // those columns are never stored.
             const int staged_rows = XB == 1 ? 1 : batch_here;
-            for (int n = 0; n < staged_rows; ++n) {
-                const int src_row = m0 + n;
-                const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(src_row) * p.x_ld +
-                                                                  static_cast<size_t>(c_begin) * kGroup);
-                if (p.x_mode == W4A16_INPUT_SILU_MUL) {
-                    const uint4* up = src + (p.K >> 3);              // the second K values of the row
-                    for (int j = tid; j < units_per_row; j += kThreads) put(silu_mul8(ldg_keep16(src + j), ldg_keep16(up + j)), j, n);
-                } else {
-                    for (int j = tid; j < units_per_row; j += kThreads) put(ldg_keep16(src + j), j, n);
+            // Up to eight rows' loads are issued before the first store (the stores are ordered against later
+            // loads, so a row-at-a-time loop would pay one L2 round trip per row).
+            constexpr int kRowBatch = XB < 8 ? XB : 8;
+            const bool silu = p.x_mode == W4A16_INPUT_SILU_MUL;
+            const uint4* base = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m0) * p.x_ld +
+                                                               static_cast<size_t>(c_begin) * kGroup);
+            const size_t row_units = static_cast<size_t>(p.x_ld) >> 3;       // 16-byte units between batch rows
+            if constexpr (XB == 1) {
+                // one row: four pieces of it per round
+                for (int j0 = tid; j0 < units_per_row; j0 += 4 * kThreads) {
+                    uint4 q[4], u[4];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const int j = j0 + r * kThreads;
+                        if (j < units_per_row) {
+                            q[r] = ldg_keep16(base + j);
+                            if (silu) u[r] = ldg_keep16(base + j + (p.K >> 3));   // the second K values of the row
+                        }
+                    }
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const int j = j0 + r * kThreads;
+                        if (j < units_per_row) put(silu ? silu_mul8(q[r], u[r]) : q[r], j, 0);
+                    }
+                }
+            } else {
+                for (int j = tid; j < units_per_row; j += kThreads) {
+                    for (int n0 = 0; n0 < staged_rows; n0 += kRowBatch) {
+                        uint4 q[kRowBatch], u[kRowBatch];
+#pragma unroll
+                        for (int r = 0; r < kRowBatch; ++r) {
+                            if (n0 + r < staged_rows) {
+                                const uint4* src = base + (n0 + r) * row_units + j;
+                                q[r] = ldg_keep16(src);
+                                if (silu) u[r] = ldg_keep16(src + (p.K >> 3));
+                            }
+                        }
+#pragma unroll
+                        for (int r = 0; r < kRowBatch; ++r) {
+                            if (n0 + r < staged_rows) put(silu ? silu_mul8(q[r], u[r]) : q[r], j, n0 + r);
+                        }
+                    }
                 }
             }
         }
