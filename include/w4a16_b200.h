@@ -98,58 +98,95 @@ int w4a16_linear_f16_config(const void* x, const void* packed, const void* scale
 /* Bytes of workspace that let w4a16_linear_f16 split K across CTAs for this problem
  * (FP32 partial sums plus arrival counters).  Never fails; returns 0 for empty problems. */
 size_t w4a16_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
+/* The same for a call made with `flags`: batches that w4a16_linear_f16 sends to the tcgen05 GEMM
+ * (M >= 65 without W4A16_FLAG_OUTPUT_F32 / W4A16_FLAG_NO_TCGEN05) or to the generic kernel need none.
+ * w4a16_linear_workspace_bytes(M, N, K) is this function with flags == 0. */
+size_t w4a16_linear_workspace_bytes_flags(int64_t M, int64_t N, int64_t K, uint32_t flags);
 
 /*
- * Tensor-parallel fan-out (no counterpart in the reference, which is single-GPU).  A layer sharded
- * over `world` GPUs of one node writes its result straight into a buffer on every GPU from the
- * kernel epilogue -- plain stores into peer-mapped memory over NVLink -- instead of handing it to a
- * collective library afterwards.  `outputs[r]` is where this rank's elements go on rank r (element
- * (m, n) lands at outputs[r][m * ld + column_offset + n]; FP16, or FP32 with W4A16_FLAG_OUTPUT_F32).
- * When every store of the launch is visible system-wide the kernel increments *send_epoch and writes
- * the new value to flags[r][rank] on every rank.  With wait_polls > 0 the launch then also waits, at
- * most that many polls per sender, until every rank has published the same epoch in this rank's
- * flags, so that its completion means "the gathered result is here"; a sender that never arrives is
- * recorded as sender + 1 in *status instead of hanging the GPU.  All pointer arrays and counters are
- * device memory; `done_counter`, `send_epoch` and `status` are single words owned by this layer on
- * this rank, zero at start.  Every rank must issue the same sequence of launches for a layer.
- * Column-parallel layers use it as an all-gather (ld = full N, column_offset = rank * N_local);
- * row-parallel layers push FP32 partials (outputs[r] = staging[r] + rank * M * N) and finish with
- * w4a16_sum_partials_f16.  Peer memory must be mapped by the caller (CUDA IPC, cuMem, or torch's
- * symmetric memory).
+ * Tensor-parallel exchange (no counterpart in the reference, which is single-GPU).  A layer sharded over
+ * `world` GPUs of one node hands its result to every GPU from the kernel epilogue -- plain stores into
+ * peer-mapped memory over NVLink -- and the kernel that consumes the result waits for it in its own
+ * prologue, after its weight prefetch is in flight.  No collective library call, no host involvement.
+ *
+ * Memory a sharded layer owns on every rank (mapped on all ranks by the caller: CUDA IPC, cuMem, or
+ * torch's symmetric memory; zero-filled at start):
+ *   two result buffers, `buffer_stride` bytes apart (publication e goes to buffer e & 1),
+ *   published[world]  uint32: published[s] = number of the latest complete publication of sender s here,
+ *   consumed[world]   uint32: consumed[c]  = latest publication that reader c has finished reading in ITS
+ *                     buffers (readers write it on every rank, so that senders learn when a buffer is free).
+ * And private device words on each rank, zero at start: done_counter, send_epoch, staged_counter, status.
+ *
+ * Sender (w4a16_peer_target): element (m, n) of this rank's result goes to
+ * outputs[r] + (e & 1) * buffer_stride, at [m * ld + column_offset + n] (FP16, or FP32 with
+ * W4A16_FLAG_OUTPUT_F32), for every rank r, e = *send_epoch + 1.  Before its first store the kernel waits
+ * (bounded) until consumed[r] >= e - 2 for all r on this rank; when all its stores are visible system-wide
+ * it sets *send_epoch = e and writes e to published[rank] on every rank.  It does not wait for the others.
+ * Column-parallel layers use it as an all-gather (ld = full N, column_offset = rank * N_local); row-parallel
+ * layers push FP32 partials (outputs[r] = staging[r] + rank * M * N floats) and finish with
+ * w4a16_sum_partials_f16.
+ *
+ * Reader (w4a16_peer_source): after the preceding kernel of the stream has completed it reads
+ * e = *epoch (the send_epoch word of the layer that produced the data, on this rank -- so that layer's
+ * launch must precede the reader in the stream), waits (bounded) until published[s] >= e for every s, reads
+ * from buffer e & 1, and when every CTA has read writes e to consumed[rank] on every rank.
+ *
+ * Every wait gives up after max_polls polls of one flag and records (which + 1) in *status -- 1..world for
+ * a sender that never published, 33..32+world for a reader that never released a buffer -- so a missing
+ * rank ends in an error the host can read, never in a hung GPU.  Every rank must issue the same sequence
+ * of launches for a layer, and every publication must be read (by one reader) on every rank.
  */
 typedef struct w4a16_peer_target {
-    void* const* outputs;
-    uint32_t* const* flags;
+    void* const* outputs;         /* [world] result buffer 0 of this layer on each rank (plus this rank's offset)   */
+    uint32_t* const* published;   /* [world] the published[] array of each rank                                      */
+    const uint32_t* consumed;     /* this rank's consumed[] array                                                     */
     uint32_t* done_counter;
     uint32_t* send_epoch;
     uint32_t* status;
+    int64_t buffer_stride;        /* bytes between result buffer 0 and 1                                              */
     int64_t ld;
     int64_t column_offset;
-    int64_t wait_polls;
+    int64_t max_polls;
     int32_t rank;
     int32_t world;
 } w4a16_peer_target;
 
-/* w4a16_linear_f16 whose result goes to every rank described by `peers` (fast path only: group 128,
- * aligned pointers; otherwise W4A16_ERR_BAD_CONFIG).  y of the plain entry point is not written. */
-int w4a16_linear_f16_peers(const void* x, const void* packed, const void* scales,
+typedef struct w4a16_peer_source {
+    const uint32_t* epoch;        /* send_epoch word of the producing layer on this rank                              */
+    const uint32_t* published;    /* this rank's published[] array of the producing layer                             */
+    uint32_t* const* consumed;    /* [world] the consumed[] array of each rank                                        */
+    uint32_t* staged_counter;
+    uint32_t* status;
+    int64_t buffer_stride;
+    int64_t max_polls;
+    int32_t rank;
+    int32_t world;
+} w4a16_peer_source;
+
+/* w4a16_linear_f16 as one stage of a tensor-parallel chain (fast path only: group 128, aligned pointers,
+ * M <= 64; otherwise W4A16_ERR_BAD_CONFIG).  `target` non-NULL: the result goes to every rank as described
+ * above and y is ignored; NULL: the result goes to y.  `source` non-NULL: x points into result buffer 0 of
+ * the producing layer on this rank and the kernel adds the parity offset after its wait; NULL: plain x.
+ * x_ld is the distance between batch rows of x in elements (>= K, a multiple of 8), so that a column slice of
+ * a wider gathered result can be the input. */
+int w4a16_linear_f16_peers(const void* x, int64_t x_ld, const void* packed, const void* scales, void* y,
                            int64_t M, int64_t N, int64_t K, int64_t group_size,
                            void* workspace, size_t workspace_bytes, uint32_t flags,
-                           const w4a16_peer_target* peers, w4a16_stream_t stream);
+                           const w4a16_peer_target* target, const w4a16_peer_source* source,
+                           w4a16_stream_t stream);
 
-/* Enqueues a one-warp kernel that waits until flags[r] has reached *wait_epoch + 1 for every
- * r < world, then stores that value to *wait_epoch.  The wait is bounded: after max_polls polls
- * (about 40 ns apart) of a sender that never arrives it gives up and records sender + 1 in *status
- * (device word, zero while healthy), so a missing rank ends in an error the host can read, not a hang. */
-int w4a16_wait_peers(const uint32_t* flags, uint32_t* wait_epoch, int32_t world, uint32_t* status,
-                     int64_t max_polls, w4a16_stream_t stream);
+/* Reader as a kernel of its own: waits for the publication described by `source`, copies `bytes` bytes
+ * (a multiple of 16) from the current result buffer (`buffer0` + parity offset) to `out` when out is
+ * non-NULL, then releases the buffer. */
+int w4a16_wait_peers(const w4a16_peer_source* source, const void* buffer0, void* out, int64_t bytes,
+                     uint32_t flags, w4a16_stream_t stream);
 
 /* y[i] = half(sum_r partials[r * count + i]), r ascending: the finish of a row-parallel layer.
- * With `flags` non-NULL every block first waits (at most max_polls polls per sender) until flags[r]
- * has reached *epoch for all r < world, reporting a missing sender in *status as above. */
+ * With `source` non-NULL `partials` is result buffer 0 of the layer and the kernel is the reader of the
+ * publication (wait, parity offset, release) as above; NULL: a plain sum over a local array.
+ * flags (here and for w4a16_wait_peers): W4A16_FLAG_PROGRAMMATIC_LAUNCH only. */
 int w4a16_sum_partials_f16(const void* partials, void* y, int64_t count, int32_t world,
-                           const uint32_t* flags, const uint32_t* epoch, uint32_t* status, int64_t max_polls,
-                           w4a16_stream_t stream);
+                           const w4a16_peer_source* source, uint32_t flags, w4a16_stream_t stream);
 
 /*
  * packed + scales -> FP16 [N, K], bit-identical to half(float(code) * float(scale)).
@@ -233,7 +270,9 @@ int w4a16_attention_decode_f16(const void* qkv, void* k_cache, void* v_cache, vo
  * splits K and so never needs scratch.
  *
  * Same arguments and results as w4a16_linear_f16 without the workspace pair.  It allocates and frees
- * nothing.  Problems whose split-K scratch exceeds the array return W4A16_ERR_TOO_LARGE and launch
+ * nothing.  Calls that need no scratch (other group sizes, misaligned pointers, batches that go to the
+ * tcgen05 GEMM) are simply forwarded.  Problems whose split-K scratch, as
+ * w4a16_linear_workspace_bytes_flags reports it, exceeds the array return W4A16_ERR_TOO_LARGE and launch
  * nothing.  All calls on a device share the one array: calls that may overlap on the GPU (several
  * streams, parallel graph branches) race; calls ordered on one stream do not.  The first call on
  * each device resolves the array's address and should be made outside stream capture.
@@ -257,7 +296,7 @@ uint64_t w4a16_launch_count(void);
 const char* w4a16_status_string(int status);
 
 /* ABI version: bumped when a signature above changes. */
-int w4a16_abi_version(void);
+int w4a16_abi_version(void);   /* currently 2 */
 
 #ifdef __cplusplus
 }

@@ -33,13 +33,31 @@ class PeerTarget(ctypes.Structure):
 
     _fields_ = [
         ("outputs", ctypes.c_void_p),
-        ("flags", ctypes.c_void_p),
+        ("published", ctypes.c_void_p),
+        ("consumed", ctypes.c_void_p),
         ("done_counter", ctypes.c_void_p),
         ("send_epoch", ctypes.c_void_p),
         ("status", ctypes.c_void_p),
+        ("buffer_stride", ctypes.c_int64),
         ("ld", ctypes.c_int64),
         ("column_offset", ctypes.c_int64),
-        ("wait_polls", ctypes.c_int64),
+        ("max_polls", ctypes.c_int64),
+        ("rank", ctypes.c_int32),
+        ("world", ctypes.c_int32),
+    ]
+
+
+class PeerSource(ctypes.Structure):
+    """Mirror of ``w4a16_peer_source``: how a kernel reads another sharded layer's published result."""
+
+    _fields_ = [
+        ("epoch", ctypes.c_void_p),
+        ("published", ctypes.c_void_p),
+        ("consumed", ctypes.c_void_p),
+        ("staged_counter", ctypes.c_void_p),
+        ("status", ctypes.c_void_p),
+        ("buffer_stride", ctypes.c_int64),
+        ("max_polls", ctypes.c_int64),
         ("rank", ctypes.c_int32),
         ("world", ctypes.c_int32),
     ]
@@ -56,14 +74,16 @@ C_API = {
         [_P, _P, _P, _P, _I, _I, _I, _I, _P, ctypes.c_size_t, ctypes.c_uint32, ctypes.POINTER(LinearConfig), _P],
     ),
     "w4a16_linear_workspace_bytes": (ctypes.c_size_t, [_I, _I, _I]),
+    "w4a16_linear_workspace_bytes_flags": (ctypes.c_size_t, [_I, _I, _I, ctypes.c_uint32]),
     "w4a16_linear_f16_static_scratch": (ctypes.c_int, [_P, _P, _P, _P, _I, _I, _I, _I, ctypes.c_uint32, _P]),
     "w4a16_static_scratch_bytes": (ctypes.c_size_t, []),
     "w4a16_linear_f16_peers": (
         ctypes.c_int,
-        [_P, _P, _P, _I, _I, _I, _I, _P, ctypes.c_size_t, ctypes.c_uint32, ctypes.POINTER(PeerTarget), _P],
+        [_P, _I, _P, _P, _P, _I, _I, _I, _I, _P, ctypes.c_size_t, ctypes.c_uint32, ctypes.POINTER(PeerTarget),
+         ctypes.POINTER(PeerSource), _P],
     ),
-    "w4a16_wait_peers": (ctypes.c_int, [_P, _P, ctypes.c_int32, _P, _I, _P]),
-    "w4a16_sum_partials_f16": (ctypes.c_int, [_P, _P, _I, ctypes.c_int32, _P, _P, _P, _I, _P]),
+    "w4a16_wait_peers": (ctypes.c_int, [ctypes.POINTER(PeerSource), _P, _P, _I, ctypes.c_uint32, _P]),
+    "w4a16_sum_partials_f16": (ctypes.c_int, [_P, _P, _I, ctypes.c_int32, ctypes.POINTER(PeerSource), ctypes.c_uint32, _P]),
     "w4a16_dequantize_f16": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
     "w4a16_quantize_pack_f16": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),
     "w4a16_quantize_pack_f32": (ctypes.c_int, [_P, _P, _P, _I, _I, _I, _P]),

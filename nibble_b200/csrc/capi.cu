@@ -32,7 +32,7 @@ bool fast_path_applies(const void* x, const void* packed, int64_t K, int64_t gro
 
 extern "C" {
 
-int w4a16_abi_version(void) { return 1; }
+int w4a16_abi_version(void) { return 2; }
 
 uint64_t w4a16_launch_count(void) { return w4a16::g_launch_count.load(std::memory_order_relaxed); }
 
@@ -51,10 +51,18 @@ const char* w4a16_status_string(int status) {
     }
 }
 
-size_t w4a16_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+size_t w4a16_linear_workspace_bytes_flags(int64_t M, int64_t N, int64_t K, uint32_t flags) {
     if (M <= 0 || N <= 0 || K <= 0 || K % w4a16::kGroupFast != 0) return 0;
+    // Calls that w4a16_linear_f16 routes away from the streaming kernel never split K: the generic kernel and the
+    // tcgen05 GEMM use no scratch.
+    if (flags & W4A16_FLAG_FORCE_GENERIC) return 0;
+    if (M >= w4a16::kTcgen05MinRows && !(flags & (W4A16_FLAG_OUTPUT_F32 | W4A16_FLAG_NO_TCGEN05))) return 0;
     const w4a16_linear_config c = w4a16::choose_linear_config(M, N, K, w4a16::kMaxKSplits);
     return w4a16::linear_workspace_bytes_for(M, N, c.k_splits);
+}
+
+size_t w4a16_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    return w4a16_linear_workspace_bytes_flags(M, N, K, 0);
 }
 
 int w4a16_linear_f16(const void* x, const void* packed, const void* scales, void* y, int64_t M, int64_t N,
@@ -148,17 +156,19 @@ int w4a16_linear_f16_config(const void* x, const void* packed, const void* scale
                                     (flags & W4A16_FLAG_OUTPUT_F32) != 0, reinterpret_cast<cudaStream_t>(stream));
 }
 
-int w4a16_linear_f16_peers(const void* x, const void* packed, const void* scales, int64_t M, int64_t N, int64_t K,
-                           int64_t group_size, void* workspace, size_t workspace_bytes, uint32_t flags,
-                           const w4a16_peer_target* peers, w4a16_stream_t stream) {
-    if (peers == nullptr) return W4A16_ERR_NULL_POINTER;
-    const int status = validate_linear(x, packed, scales, peers, M, N, K, group_size);
+int w4a16_linear_f16_peers(const void* x, int64_t x_ld, const void* packed, const void* scales, void* y, int64_t M,
+                           int64_t N, int64_t K, int64_t group_size, void* workspace, size_t workspace_bytes,
+                           uint32_t flags, const w4a16_peer_target* target, const w4a16_peer_source* source,
+                           w4a16_stream_t stream) {
+    // with a target the results go to the ranks' buffers and y is not used
+    const int status = validate_linear(x, packed, scales, target != nullptr ? static_cast<const void*>(target) : y, M, N,
+                                       K, group_size);
     if (status != W4A16_OK) return status;
     if (M == 0 || N == 0 || K == 0) return W4A16_ERR_BAD_SHAPE;
-    if (!fast_path_applies(x, packed, K, group_size)) return W4A16_ERR_BAD_CONFIG;
+    if (M > 64 || !fast_path_applies(x, packed, K, group_size)) return W4A16_ERR_BAD_CONFIG;
     w4a16::LinearProblem p{static_cast<const __half*>(x), static_cast<const uint8_t*>(packed),
-                           static_cast<const __half*>(scales), nullptr, M, N, K, group_size,
-                           workspace, workspace_bytes, peers};
+                           static_cast<const __half*>(scales), target != nullptr ? nullptr : y, M, N, K, group_size,
+                           workspace, workspace_bytes, target, nullptr, source, x_ld};
     int max_splits = 1;
     if (workspace != nullptr && aligned16(workspace)) {
         for (int splits = w4a16::kMaxKSplits; splits > 1; splits >>= 1) {
@@ -174,21 +184,20 @@ int w4a16_linear_f16_peers(const void* x, const void* packed, const void* scales
                                     (flags & W4A16_FLAG_OUTPUT_F32) != 0, reinterpret_cast<cudaStream_t>(stream));
 }
 
-int w4a16_wait_peers(const uint32_t* flags, uint32_t* wait_epoch, int32_t world, uint32_t* status, int64_t max_polls,
+int w4a16_wait_peers(const w4a16_peer_source* source, const void* buffer0, void* out, int64_t bytes, uint32_t flags,
                      w4a16_stream_t stream) {
-    if (flags == nullptr || wait_epoch == nullptr || status == nullptr) return W4A16_ERR_NULL_POINTER;
-    if (max_polls <= 0) return W4A16_ERR_BAD_SHAPE;
-    return w4a16::launch_wait_peers(flags, wait_epoch, world, status, max_polls, reinterpret_cast<cudaStream_t>(stream));
+    return w4a16::launch_wait_peers(source, buffer0, out, bytes, (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0,
+                                    reinterpret_cast<cudaStream_t>(stream));
 }
 
-int w4a16_sum_partials_f16(const void* partials, void* y, int64_t count, int32_t world, const uint32_t* flags,
-                           const uint32_t* epoch, uint32_t* status, int64_t max_polls, w4a16_stream_t stream) {
+int w4a16_sum_partials_f16(const void* partials, void* y, int64_t count, int32_t world, const w4a16_peer_source* source,
+                           uint32_t flags, w4a16_stream_t stream) {
     if (count < 0 || world < 1 || world > 32) return W4A16_ERR_BAD_SHAPE;
     if (count == 0) return W4A16_OK;
     if (partials == nullptr || y == nullptr) return W4A16_ERR_NULL_POINTER;
-    if (flags != nullptr && (epoch == nullptr || status == nullptr || max_polls <= 0)) return W4A16_ERR_NULL_POINTER;
-    return w4a16::launch_sum_partials(static_cast<const float*>(partials), static_cast<__half*>(y), count, world, flags,
-                                      epoch, status, max_polls, reinterpret_cast<cudaStream_t>(stream));
+    if (source != nullptr && source->world != world) return W4A16_ERR_BAD_SHAPE;
+    return w4a16::launch_sum_partials(static_cast<const float*>(partials), static_cast<__half*>(y), count, world, source,
+                                      (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int w4a16_device_status(uint32_t* value) {

@@ -97,7 +97,7 @@ at::Tensor linear_impl(const at::Tensor& activations, const at::Tensor& packed_w
 
     void* workspace = nullptr;
     size_t workspace_bytes = 0;
-    const size_t wanted = w4a16_linear_workspace_bytes(m, n, k);
+    const size_t wanted = w4a16_linear_workspace_bytes_flags(m, n, k, flags);
     if (wanted > 0 && wanted <= static_cast<size_t>(kWorkspaceBytes)) {
         at::Tensor& ws = workspace_for(activations.device(), stream);
         workspace = ws.data_ptr();

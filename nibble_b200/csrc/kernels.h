@@ -29,6 +29,8 @@ struct LinearProblem {
     size_t workspace_bytes;
     const w4a16_peer_target* peers = nullptr;   // fan the result out to a tensor-parallel group
     const w4a16_input_transform* input = nullptr;   // x is derived from other buffers while it is staged
+    const w4a16_peer_source* source = nullptr;  // x is another sharded layer's published result
+    int64_t x_ld = 0;                           // elements between batch rows of x (0: K)
 };
 
 // Workspace layout for split-K: arrival counters first, FP32 partials after them.
@@ -52,12 +54,12 @@ constexpr int kTcgen05MinRows = 65;     // smaller batches stay on the mma.sync 
 // Any even group size, any alignment, any M.
 int launch_linear_generic(const LinearProblem& p, bool out_f32, cudaStream_t stream);
 
-// Tensor-parallel helpers: bounded wait for every rank's publication, and the rank-ordered sum of
-// FP32 partials into FP16.
-int launch_wait_peers(const unsigned* flags, unsigned* wait_epoch, int world, unsigned* status, long long max_polls,
+// Tensor-parallel helpers: a reader kernel (bounded wait for every rank's publication, optional copy, release)
+// and the rank-ordered sum of FP32 partials into FP16.
+int launch_wait_peers(const w4a16_peer_source* source, const void* buffer0, void* out, int64_t bytes, bool programmatic,
                       cudaStream_t stream);
-int launch_sum_partials(const float* partials, __half* y, int64_t count, int world, const unsigned* flags,
-                        const unsigned* epoch, unsigned* status, long long max_polls, cudaStream_t stream);
+int launch_sum_partials(const float* partials, __half* y, int64_t count, int world, const w4a16_peer_source* source,
+                        bool programmatic, cudaStream_t stream);
 
 int launch_dequantize(const uint8_t* packed, const __half* scales, __half* weights, int64_t N,
                       int64_t K, int64_t group, cudaStream_t stream);

@@ -35,8 +35,11 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <atomic>
 #include <map>
 #include <mutex>
+#include <tuple>
 #include <utility>
 
 #include "kernels.h"
@@ -65,15 +68,23 @@ struct MmaParams {
     int row_tiles_total;   // ceil(N / (16 * TILES))
     int out_f32;
     // Optional fan-out of the result to every GPU of a tensor-parallel group (null: plain y).
-    void* const* peer_out;          // [world] where this rank's results go on each rank
-    unsigned* const* peer_flags;    // [world] each rank's arrival flags, indexed by sender
+    void* const* peer_out;          // [world] result buffer 0 of this layer on each rank
+    unsigned* const* peer_flags;    // [world] each rank's published[] flags, indexed by sender
+    const unsigned* consumed;       // this rank's consumed[] flags, indexed by reader
     unsigned* done_counter;         // CTAs of this launch that finished; left at zero
-    unsigned* send_epoch;           // launches published so far by this layer on this rank
-    unsigned* peer_status;          // zero while healthy; sender + 1 when a wait gave up on a sender
+    unsigned* send_epoch;           // publications made so far by this layer on this rank
+    unsigned* peer_status;          // zero while healthy; see wait_for_flags
+    long long out_stride;           // bytes between the two result buffers (publication e uses buffer e & 1)
     long long ld_out;               // elements between batch rows of the peers' buffers
     long long col_out;              // first column this rank writes there
-    long long wait_polls;           // > 0: also wait (bounded) for every rank's publication of this epoch
+    long long wait_polls;           // bound of every flag wait
     int rank, world;
+    // Optional: x is the published result of another sharded layer (null: plain x).
+    const unsigned* src_epoch;      // that layer's send_epoch word on this rank
+    const unsigned* src_published;  // this rank's published[] flags of that layer
+    unsigned* const* src_consumed;  // [world] consumed[] flags of that layer on each rank
+    unsigned* staged_counter;       // CTAs of this launch that have read x; left at zero
+    long long src_stride;           // bytes between that layer's two result buffers
     // Activations derived while they are staged (W4A16_INPUT_*): see the staging code.
     int x_mode;
     long long x_ld;                 // elements between batch rows of x (2K for [gate | up] rows)
@@ -112,22 +123,34 @@ __device__ __forceinline__ uint4 silu_mul8(const uint4& gate, const uint4& up) {
     return as_uint4(out);
 }
 
-// Bounded wait until flags[sender] has reached `epoch` for every sender; a sender that never arrives
-// is recorded in *status (sender + 1) and the wait moves on.
-__device__ __forceinline__ void wait_for_senders(const unsigned* flags, int world, unsigned epoch,
-                                                 long long max_polls, unsigned* status) {
-    for (int sender = 0; sender < world; ++sender) {
+// Bounded wait, by the first `world` lanes of one warp, until flags[lane] has reached `epoch`.  A flag that
+// never gets there is recorded in *status as code_base + lane + 1 and the wait moves on: the caller then
+// computes on unfinished data and the host reads the status word, but the GPU never hangs.
+__device__ __forceinline__ void wait_for_flags(const unsigned* flags, int world, unsigned epoch, long long max_polls,
+                                               unsigned* status, unsigned code_base) {
+    const int lane = threadIdx.x & 31;
+    if (lane < world) {
         bool arrived = false;
         for (long long poll = 0; poll < max_polls; ++poll) {
             unsigned seen;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + sender) : "memory");
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + lane) : "memory");
             if (static_cast<int>(seen - epoch) >= 0) {
                 arrived = true;
                 break;
             }
-            __nanosleep(32);
+            __nanosleep(20);
         }
-        if (!arrived) atomicMax(status, static_cast<unsigned>(sender) + 1u);
+        if (!arrived && status != nullptr) atomicMax(status, code_base + static_cast<unsigned>(lane) + 1u);
+    }
+    __syncwarp();
+}
+constexpr unsigned kReaderCodeBase = 32;   // status codes 33.. name a reader that never released a buffer
+
+// Tells every rank that this rank has finished reading publication `epoch` of a layer.  The reads are
+// complete (their values have been used) before the caller gets here, so a relaxed store is enough.
+__device__ __forceinline__ void release_buffers(unsigned* const* consumed, int rank, int world, unsigned epoch) {
+    for (int peer = 0; peer < world; ++peer) {
+        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(consumed[peer] + rank), "r"(epoch) : "memory");
     }
 }
 
@@ -336,6 +359,26 @@ linear_mma_kernel(const MmaParams p) {
     pdl_release_downstream();
     pdl_wait_for_upstream();
 
+    // Tensor-parallel hand-shakes, with the weight ring already in flight: as a reader, wait until every
+    // rank's part of x has landed here; as a sender, until every rank has let go of the result buffer this
+    // launch will overwrite (two publications back, so this is normally satisfied long ago).
+    const __half* x_in = p.x;
+    unsigned src_epoch = 0, out_epoch = 0;
+    size_t out_offset = 0;
+    if (p.src_epoch != nullptr || p.peer_out != nullptr) {
+        if (p.src_epoch != nullptr) {
+            src_epoch = __ldcg(p.src_epoch);
+            if (warp == 0) wait_for_flags(p.src_published, p.world, src_epoch, p.wait_polls, p.peer_status, 0u);
+            x_in = reinterpret_cast<const __half*>(reinterpret_cast<const char*>(p.x) + (src_epoch & 1u) * p.src_stride);
+        }
+        if (p.peer_out != nullptr) {
+            out_epoch = __ldcg(p.send_epoch) + 1u;
+            if (warp == 1) wait_for_flags(p.consumed, p.world, out_epoch - 2u, p.wait_polls, p.peer_status, kReaderCodeBase);
+            out_offset = static_cast<size_t>(out_epoch & 1u) * static_cast<size_t>(p.out_stride);
+        }
+        __syncthreads();
+    }
+
     // ---- stage this CTA's slice of x in shared memory, in B-fragment order --------------------
     // 16-byte unit ((c * 4 + i) * XB + n) * 4 + t holds, for batch row n, the eight activations
     // k = c*128 + t*32 + i*8 .. +8 re-paired as (x0,x4)(x1,x5)(x2,x6)(x3,x7).
@@ -354,7 +397,7 @@ linear_mma_kernel(const MmaParams p) {
         };
         if (p.x_mode == W4A16_INPUT_ADD_RMSNORM) {
             // pass 1, whole row: s = half(stream + delta), sum of squares in FP32
-            const uint4* s_in = reinterpret_cast<const uint4*>(p.x);
+            const uint4* s_in = reinterpret_cast<const uint4*>(x_in);
             const uint4* d_in = reinterpret_cast<const uint4*>(p.x_second);
             const bool writer = p.stream_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
             auto summed = [&](int j) {
@@ -408,7 +451,7 @@ linear_mma_kernel(const MmaParams p) {
             // loads, so a row-at-a-time loop would pay one L2 round trip per row).
             constexpr int kRowBatch = XB < 8 ? XB : 8;
             const bool silu = p.x_mode == W4A16_INPUT_SILU_MUL;
-            const uint4* base = reinterpret_cast<const uint4*>(p.x + static_cast<size_t>(m0) * p.x_ld +
+            const uint4* base = reinterpret_cast<const uint4*>(x_in + static_cast<size_t>(m0) * p.x_ld +
                                                                static_cast<size_t>(c_begin) * kGroup);
             const size_t row_units = static_cast<size_t>(p.x_ld) >> 3;       // 16-byte units between batch rows
             if constexpr (XB == 1) {
@@ -451,6 +494,14 @@ linear_mma_kernel(const MmaParams p) {
         }
     }
     __syncthreads();
+    if (p.src_epoch != nullptr && tid == 0) {
+        // the last CTA to have read its part of x gives the buffer back to the senders
+        const unsigned ctas = gridDim.x * gridDim.y * gridDim.z;
+        if (atomicAdd(p.staged_counter, 1u) == ctas - 1) {
+            *p.staged_counter = 0u;
+            release_buffers(p.src_consumed, p.rank, p.world, src_epoch);
+        }
+    }
 
     // B-fragment base of this lane: batch column g of n-tile 0 (every lane reads row 0 when XB == 1).
     const unsigned x_lane = xs + static_cast<unsigned>(w_begin - c_begin) * (XB * 256) +
@@ -602,10 +653,11 @@ linear_mma_kernel(const MmaParams p) {
         } else {
             const size_t at = m * static_cast<size_t>(p.ld_out) + static_cast<size_t>(p.col_out) + row;
             for (int peer = 0; peer < p.world; ++peer) {
+                char* buffer = static_cast<char*>(p.peer_out[peer]) + out_offset;
                 if (p.out_f32) {
-                    static_cast<float*>(p.peer_out[peer])[at] = sum;
+                    reinterpret_cast<float*>(buffer)[at] = sum;
                 } else {
-                    static_cast<__half*>(p.peer_out[peer])[at] = __float2half_rn(sum);
+                    reinterpret_cast<__half*>(buffer)[at] = __float2half_rn(sum);
                 }
             }
         }
@@ -779,67 +831,91 @@ linear_mma_kernel(const MmaParams p) {
 
     if (p.peer_out != nullptr) {
         // Publish: once every CTA of the launch has made its peer stores visible system-wide, the
-        // last one to finish bumps this layer's epoch and writes it to flags[rank] on every rank.
+        // last one to finish records the publication and writes its number to published[rank] on every rank.
         __syncthreads();
         if (tid == 0) {
             __threadfence_system();
             const unsigned ctas = gridDim.x * gridDim.y * gridDim.z;
             if (atomicAdd(p.done_counter, 1u) == ctas - 1) {
                 *p.done_counter = 0u;
-                const unsigned epoch = *p.send_epoch + 1u;
-                *p.send_epoch = epoch;
+                *p.send_epoch = out_epoch;
                 __threadfence_system();
                 for (int peer = 0; peer < p.world; ++peer) {
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[peer] + p.rank), "r"(epoch)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[peer] + p.rank), "r"(out_epoch)
                                  : "memory");
-                }
-                // Optionally the launch itself completes only when every rank's part has landed here.
-                if (p.wait_polls > 0) {
-                    wait_for_senders(p.peer_flags[p.rank], p.world, epoch, p.wait_polls, p.peer_status);
                 }
             }
         }
     }
 }
 
-// Waits (bounded) until every rank has published at least the epoch this rank expects next for the
-// layer, i.e. until all slices of the gathered result have landed in this rank's buffer.
-__global__ void wait_peers_kernel(const unsigned* flags, unsigned* wait_epoch, int world, unsigned* status,
-                                  long long max_polls) {
-    const int lane = threadIdx.x;
-    const unsigned expected = *wait_epoch + 1u;
-    bool ok = true;
-    if (lane < world) {
-        ok = false;
-        for (long long poll = 0; poll < max_polls; ++poll) {
-            unsigned seen;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flags + lane) : "memory");
-            if (static_cast<int>(seen - expected) >= 0) {
-                ok = true;
-                break;
-            }
-            __nanosleep(40);
+// What a kernel needs to be the reader of a sharded layer's publication.
+struct ReaderParams {
+    const unsigned* epoch;
+    const unsigned* published;
+    unsigned* const* consumed;
+    unsigned* staged_counter;
+    unsigned* status;
+    long long stride;
+    long long max_polls;
+    int rank, world;
+};
+
+// Block-wide: waits (bounded) for the publication, returns its number; every thread gets it.
+__device__ __forceinline__ unsigned reader_wait(const ReaderParams& r) {
+    const unsigned epoch = __ldcg(r.epoch);
+    if (threadIdx.x < 32) wait_for_flags(r.published, r.world, epoch, r.max_polls, r.status, 0u);
+    __syncthreads();
+    return epoch;
+}
+
+// Block-wide: the last block of the grid to get here gives the buffers back to the senders.
+__device__ __forceinline__ void reader_release(const ReaderParams& r, unsigned epoch) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned blocks = gridDim.x * gridDim.y * gridDim.z;
+        if (atomicAdd(r.staged_counter, 1u) == blocks - 1) {
+            *r.staged_counter = 0u;
+            release_buffers(r.consumed, r.rank, r.world, epoch);
         }
-        if (!ok) atomicMax(status, static_cast<unsigned>(lane) + 1u);   // which sender never arrived
     }
-    __syncwarp();
-    if (lane == 0) *wait_epoch = expected;
+}
+
+// A reader as a kernel of its own: waits for the publication, optionally copies it out of the result buffer
+// (16-byte units), releases the buffer.
+__global__ void wait_peers_kernel(const ReaderParams r, const uint4* buffer0, uint4* out, long long units) {
+    pdl_release_downstream();
+    pdl_wait_for_upstream();
+    const unsigned epoch = reader_wait(r);
+    if (out != nullptr) {
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(buffer0) + (epoch & 1u) * r.stride);
+        for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < units;
+             i += static_cast<long long>(gridDim.x) * blockDim.x) {
+            out[i] = __ldcg(src + i);
+        }
+    }
+    reader_release(r, epoch);
 }
 
 // y = half(sum over ranks of partials[rank]), summed in rank order so every rank gets identical bits.
-// With `flags` the block first waits (bounded) until every rank has published *epoch.
+// With a reader description the block first waits (bounded) for every rank's publication, reads the
+// partials of that publication's buffer and releases it afterwards.
 __global__ void sum_partials_kernel(const float* __restrict__ partials, __half* __restrict__ y, long long count,
-                                    int world, const unsigned* flags, const unsigned* epoch, unsigned* status,
-                                    long long max_polls) {
-    if (flags != nullptr) {
-        if (threadIdx.x == 0) wait_for_senders(flags, world, *epoch, max_polls, status);
-        __syncthreads();
+                                    int world, const ReaderParams r) {
+    pdl_release_downstream();
+    pdl_wait_for_upstream();
+    unsigned epoch = 0;
+    if (r.epoch != nullptr) {
+        epoch = reader_wait(r);
+        partials = reinterpret_cast<const float*>(reinterpret_cast<const char*>(partials) + (epoch & 1u) * r.stride);
     }
     const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= count) return;
-    float sum = 0.f;
-    for (int r = 0; r < world; ++r) sum += __ldcg(partials + static_cast<long long>(r) * count + i);
-    y[i] = __float2half_rn(sum);
+    if (i < count) {
+        float sum = 0.f;
+        for (int k = 0; k < world; ++k) sum += __ldcg(partials + static_cast<long long>(k) * count + i);
+        y[i] = __float2half_rn(sum);
+    }
+    if (r.epoch != nullptr) reader_release(r, epoch);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -913,18 +989,18 @@ bool pick_variant(int nt, bool single_row, const w4a16_linear_config& c, Variant
 int batch_tiles_for(int64_t M) { return M <= 8 ? 1 : (M <= 16 ? 2 : 4); }
 int x_rows_for(int64_t M) { return M == 1 ? 1 : 8 * batch_tiles_for(M); }
 
-int sm_count() {
-    static int cached = 0;
-    if (cached == 0) {
-        int device = 0, count = 0;
-        if (cudaGetDevice(&device) == cudaSuccess &&
-            cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && count > 0) {
-            cached = count;
-        } else {
-            return 148;
-        }
+constexpr int kMaxDevices = 64;
+
+// SM count of `device`, looked up once per device.
+int sm_count(int device) {
+    static std::atomic<int> cached[kMaxDevices] = {};
+    if (device < 0 || device >= kMaxDevices) return 148;
+    int count = cached[device].load(std::memory_order_relaxed);
+    if (count == 0) {
+        if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) return 148;
+        cached[device].store(count, std::memory_order_relaxed);
     }
-    return cached;
+    return count;
 }
 
 // Bytes of x a CTA holds for `rows` stored batch rows of a K slice of `chunks` chunks.
@@ -1012,26 +1088,70 @@ w4a16_linear_config choose_linear_config(int64_t M, int64_t N, int64_t K, int ma
     return c;
 }
 
-int launch_wait_peers(const unsigned* flags, unsigned* wait_epoch, int world, unsigned* status, long long max_polls,
-                      cudaStream_t stream) {
-    if (world < 1 || world > 32) return W4A16_ERR_BAD_SHAPE;
-    wait_peers_kernel<<<1, 32, 0, stream>>>(flags, wait_epoch, world, status, max_polls);
-    if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
+namespace {
+
+int reader_params(const w4a16_peer_source* source, ReaderParams* r) {
+    *r = ReaderParams{};
+    if (source == nullptr) return W4A16_OK;
+    if (source->epoch == nullptr || source->published == nullptr || source->consumed == nullptr ||
+        source->staged_counter == nullptr || source->status == nullptr) {
+        return W4A16_ERR_NULL_POINTER;
+    }
+    if (source->world < 1 || source->world > 32 || source->rank < 0 || source->rank >= source->world ||
+        source->max_polls <= 0 || source->buffer_stride < 0) {
+        return W4A16_ERR_BAD_SHAPE;
+    }
+    *r = ReaderParams{source->epoch, source->published, source->consumed, source->staged_counter, source->status,
+                      source->buffer_stride, source->max_polls, source->rank, source->world};
+    return W4A16_OK;
+}
+
+template <typename Kernel, typename... Args>
+int launch_small(Kernel kernel, unsigned blocks, unsigned threads, bool programmatic, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t launch = {};
+    launch.gridDim = dim3(blocks, 1, 1);
+    launch.blockDim = dim3(threads, 1, 1);
+    launch.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    launch.attrs = attr;
+    launch.numAttrs = programmatic ? 1 : 0;
+    if (cudaLaunchKernelEx(&launch, kernel, args...) != cudaSuccess) return W4A16_ERR_LAUNCH;
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return W4A16_OK;
 }
 
-int launch_sum_partials(const float* partials, __half* y, int64_t count, int world, const unsigned* flags,
-                        const unsigned* epoch, unsigned* status, long long max_polls, cudaStream_t stream) {
+}  // namespace
+
+int launch_wait_peers(const w4a16_peer_source* source, const void* buffer0, void* out, int64_t bytes, bool programmatic,
+                      cudaStream_t stream) {
+    if (source == nullptr) return W4A16_ERR_NULL_POINTER;
+    ReaderParams r;
+    const int status = reader_params(source, &r);
+    if (status != W4A16_OK) return status;
+    if (bytes < 0 || bytes % 16 != 0) return W4A16_ERR_BAD_SHAPE;
+    if (out != nullptr && (buffer0 == nullptr || reinterpret_cast<uintptr_t>(buffer0) % 16 != 0 ||
+                           reinterpret_cast<uintptr_t>(out) % 16 != 0 || source->buffer_stride % 16 != 0)) {
+        return W4A16_ERR_MISALIGNED;
+    }
+    const long long units = out != nullptr ? bytes / 16 : 0;
+    const unsigned blocks = static_cast<unsigned>(std::min<long long>(32, std::max<long long>(1, (units + 255) / 256)));
+    return launch_small(wait_peers_kernel, blocks, 256, programmatic, stream, r, static_cast<const uint4*>(buffer0),
+                        static_cast<uint4*>(out), units);
+}
+
+int launch_sum_partials(const float* partials, __half* y, int64_t count, int world, const w4a16_peer_source* source,
+                        bool programmatic, cudaStream_t stream) {
     if (count <= 0) return W4A16_OK;
+    ReaderParams r;
+    const int status = reader_params(source, &r);
+    if (status != W4A16_OK) return status;
     const int threads = 256;
     const int64_t blocks = (count + threads - 1) / threads;
     if (blocks > INT32_MAX) return W4A16_ERR_TOO_LARGE;
-    sum_partials_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(partials, y, count, world, flags, epoch,
-                                                                               status, max_polls);
-    if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
-    g_launch_count.fetch_add(1, std::memory_order_relaxed);
-    return W4A16_OK;
+    return launch_small(sum_partials_kernel, static_cast<unsigned>(blocks), threads, programmatic, stream, partials, y,
+                        static_cast<long long>(count), world, r);
 }
 
 int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_in, bool programmatic,
@@ -1119,23 +1239,55 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
         }
         params.x_mode = in.kind;
     }
+    params.consumed = nullptr;
+    params.out_stride = 0;
+    params.src_epoch = nullptr;
+    params.src_published = nullptr;
+    params.src_consumed = nullptr;
+    params.staged_counter = nullptr;
+    params.src_stride = 0;
+    if (prob.x_ld != 0) {
+        if (prob.x_ld < prob.K || prob.x_ld % 8 != 0 || params.x_mode != W4A16_INPUT_PLAIN) return W4A16_ERR_BAD_SHAPE;
+        params.x_ld = prob.x_ld;
+    }
     if (prob.peers != nullptr) {
         const w4a16_peer_target& t = *prob.peers;
-        if (t.outputs == nullptr || t.flags == nullptr || t.done_counter == nullptr || t.send_epoch == nullptr ||
-            t.world < 1 || t.world > 32 || t.rank < 0 || t.rank >= t.world || t.ld < prob.N || t.column_offset < 0) {
+        if (t.outputs == nullptr || t.published == nullptr || t.consumed == nullptr || t.done_counter == nullptr ||
+            t.send_epoch == nullptr || t.status == nullptr) {
+            return W4A16_ERR_NULL_POINTER;
+        }
+        if (t.world < 1 || t.world > 32 || t.rank < 0 || t.rank >= t.world || t.ld < prob.N || t.column_offset < 0 ||
+            t.max_polls <= 0 || t.buffer_stride < 0) {
             return W4A16_ERR_BAD_SHAPE;
         }
         params.peer_out = t.outputs;
-        params.peer_flags = t.flags;
+        params.peer_flags = t.published;
+        params.consumed = t.consumed;
         params.done_counter = t.done_counter;
         params.send_epoch = t.send_epoch;
-        if (t.wait_polls > 0 && t.status == nullptr) return W4A16_ERR_NULL_POINTER;
         params.peer_status = t.status;
-        params.wait_polls = t.wait_polls;
+        params.out_stride = t.buffer_stride;
+        params.wait_polls = t.max_polls;
         params.ld_out = t.ld;
         params.col_out = t.column_offset;
         params.rank = t.rank;
         params.world = t.world;
+    }
+    if (prob.source != nullptr) {
+        ReaderParams r;
+        const int status = reader_params(prob.source, &r);
+        if (status != W4A16_OK) return status;
+        if (params.x_mode != W4A16_INPUT_PLAIN || r.stride % 16 != 0) return W4A16_ERR_BAD_CONFIG;
+        if (prob.peers != nullptr && (prob.peers->world != r.world || prob.peers->rank != r.rank)) return W4A16_ERR_BAD_SHAPE;
+        params.src_epoch = r.epoch;
+        params.src_published = r.published;
+        params.src_consumed = r.consumed;
+        params.staged_counter = r.staged_counter;
+        params.src_stride = r.stride;
+        params.rank = r.rank;
+        params.world = r.world;
+        if (params.peer_status == nullptr) params.peer_status = r.status;
+        if (params.wait_polls == 0) params.wait_polls = r.max_polls;
     }
     if (splits > 1) {
         const size_t need = linear_workspace_bytes_for(prob.M, prob.N, splits);
@@ -1150,14 +1302,17 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
                         static_cast<size_t>(variant.stages) * variant.stage_bytes;
     if (smem > static_cast<size_t>(kSmemBudget)) return W4A16_ERR_WORKSPACE;   // x slice too large: more K splits
 
-    // Opt in to large dynamic shared memory once per kernel variant, and learn its occupancy
-    // (cached per variant and shared-memory size; one process drives one device).
+    // Opt in to large dynamic shared memory once per device and kernel variant (the attribute belongs to
+    // the function as loaded on one device), and learn its occupancy there (cached per device, variant
+    // and shared-memory size).
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return W4A16_ERR_LAUNCH;
     static std::mutex mutex;
-    static std::map<std::pair<const void*, size_t>, int> occupancy;
+    static std::map<std::tuple<int, const void*, size_t>, int> occupancy;
     int blocks_per_sm = 0;
     {
         std::lock_guard<std::mutex> lock(mutex);
-        const auto key = std::make_pair(variant.fn, smem);
+        const auto key = std::make_tuple(device, variant.fn, smem);
         const auto found = occupancy.find(key);
         if (found != occupancy.end()) {
             blocks_per_sm = found->second;
@@ -1178,7 +1333,7 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
     const int64_t batch_blocks = (prob.M + 8 * nt - 1) / (8 * nt);
     if (batch_blocks > 65535) return W4A16_ERR_TOO_LARGE;
     const int64_t tile_ctas = (params.row_tiles_total + rw - 1) / rw;
-    int64_t resident = static_cast<int64_t>(sm_count()) * blocks_per_sm / (splits * batch_blocks);
+    int64_t resident = static_cast<int64_t>(sm_count(device)) * blocks_per_sm / (splits * batch_blocks);
     if (resident < 1) resident = 1;
     const int64_t grid_x = tile_ctas < resident ? tile_ctas : resident;
     const dim3 grid(static_cast<unsigned>(grid_x), static_cast<unsigned>(splits), static_cast<unsigned>(batch_blocks));

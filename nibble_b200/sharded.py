@@ -132,63 +132,149 @@ class RowParallelQuantizedLinear(torch.nn.Module):
 
 
 # ---------------------------------------------------------------------------------------------
-# Exchange fused into the kernel epilogue: results are stored straight into every rank's buffer
-# over NVLink (peer-mapped memory), followed by a flag; no collective-library call per layer.
+# Exchange fused into the kernels: a sender's epilogue stores its result straight into a buffer on
+# every rank over NVLink (peer-mapped memory) and raises a flag there; the kernel that consumes the
+# result waits for the flags in its own prologue, with its weight prefetch already in flight, and
+# gives the buffer back with a second set of flags.  No collective-library call per layer.
+# The protocol is described beside w4a16_peer_target / w4a16_peer_source in include/w4a16_b200.h.
 # ---------------------------------------------------------------------------------------------
 import ctypes
 
 from . import _native
 
 _MAX_POLLS = 2_000_000   # bounded device-side wait: roughly a second before a missing rank is reported
+_FLAG_BYTES = 512        # published[world] at +0, consumed[world] at +256
 
 
 def _stream_ptr() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-class _PeerRegion:
-    """One symmetric allocation per layer: [result bytes | 256 bytes of arrival flags], mapped on
-    every rank of the group, plus this rank's private counters (done, send epoch, wait epoch, status)."""
+def _launch_flags() -> int:
+    return _native.FLAG_PROGRAMMATIC_LAUNCH if _cuda.programmatic_launch_enabled() else 0
 
-    def __init__(self, result_bytes: int, process_group) -> None:
-        import torch.distributed._symmetric_memory as symm
 
-        self.group = process_group if process_group is not None else dist.group.WORLD
-        self.rank = dist.get_rank(self.group)
-        self.world = dist.get_world_size(self.group)
+class LocalRanks:
+    """Stand-in for a process group when all ``world`` ranks of a sharded layer live in ONE process on
+    ONE GPU (tests, single-GPU bring-up): the "peer" buffers are ordinary device tensors.  The ranks'
+    kernels then run one after the other on a stream, so every rank's senders must be launched before
+    any rank's readers."""
+
+    def __init__(self, world: int):
+        self.world = world
+        self._regions: dict = {}
+
+    def buffers(self, key, nbytes: int, device) -> list[torch.Tensor]:
+        """The ``world`` regions of the layer called ``key`` (created at the first rank's request)."""
+        if key not in self._regions:
+            self._regions[key] = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(self.world)]
+        return self._regions[key]
+
+
+class PeerRegion:
+    """Memory of one sharded layer on this rank: ``[result buffer 0 | result buffer 1 | published[world] |
+    consumed[world]]`` in memory every rank can write (torch symmetric memory, or plain tensors with
+    ``LocalRanks``), plus this rank's private words (done, send epoch, staged, status)."""
+
+    def __init__(self, result_bytes: int, process_group=None, *, local: LocalRanks | None = None, rank: int | None = None,
+                 key=None, max_polls: int = _MAX_POLLS) -> None:
         self.result_bytes = (result_bytes + 255) // 256 * 256
+        self.max_polls = int(max_polls)
         device = torch.device("cuda", torch.cuda.current_device())
-        self.buffer = symm.empty((self.result_bytes + 256,), dtype=torch.uint8, device=device)
-        self.buffer.zero_()
-        self.handle = symm.rendezvous(self.buffer, self.group)
-        self.peer_base = [int(p) for p in self.handle.buffer_ptrs]
-        self.flag_table = torch.tensor([p + self.result_bytes for p in self.peer_base], dtype=torch.int64, device=device)
-        self.counters = torch.zeros(4, dtype=torch.int32, device=device)   # done, send epoch, wait epoch, status
-        torch.cuda.synchronize()
-        dist.barrier(group=self.group)   # every rank's flags are zero before anyone publishes
+        total = 2 * self.result_bytes + _FLAG_BYTES
+        if local is not None:
+            self.rank, self.world = int(rank), local.world
+            buffers = local.buffers(key, total, device)
+            self.buffer = buffers[self.rank]
+            self.peer_base = [int(b.data_ptr()) for b in buffers]
+            self._keep = buffers
+        else:
+            import torch.distributed._symmetric_memory as symm
 
-    def table(self, byte_offset_for_rank) -> torch.Tensor:
-        """Device array of per-rank destinations: peer base + byte_offset_for_rank(r)."""
-        return torch.tensor([p + byte_offset_for_rank(r) for r, p in enumerate(self.peer_base)],
-                            dtype=torch.int64, device=self.buffer.device)
+            group = process_group if process_group is not None else dist.group.WORLD
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+            self.buffer = symm.empty((total,), dtype=torch.uint8, device=device)
+            self.buffer.zero_()
+            handle = symm.rendezvous(self.buffer, group)
+            self.peer_base = [int(p) for p in handle.buffer_ptrs]
+            self._keep = handle
+            torch.cuda.synchronize()
+            dist.barrier(group=group)   # every rank's flags are zero before anyone publishes
+        if self.world > 32:
+            raise ValueError("at most 32 ranks")
+        flags0 = 2 * self.result_bytes
+        i64 = dict(dtype=torch.int64, device=device)
+        self._published_table = torch.tensor([p + flags0 for p in self.peer_base], **i64)
+        self._consumed_table = torch.tensor([p + flags0 + 256 for p in self.peer_base], **i64)
+        self.counters = torch.zeros(4, dtype=torch.int32, device=device)   # done, send epoch, staged, status
+        self._tables: dict = {}
 
-    def target(self, out_table: torch.Tensor, ld: int, column_offset: int, wait: bool) -> _native.PeerTarget:
-        c = self.counters.data_ptr()
-        return _native.PeerTarget(out_table.data_ptr(), self.flag_table.data_ptr(), c, c + 4, c + 12, ld, column_offset,
-                                  _MAX_POLLS if wait else 0, self.rank, self.world)
+    # addresses on this rank
+    @property
+    def base(self) -> int:
+        return self.buffer.data_ptr()
 
-    def wait(self) -> None:
-        c = self.counters.data_ptr()
-        status = _native.core().w4a16_wait_peers(self.buffer.data_ptr() + self.result_bytes, c + 8, self.world, c + 12,
-                                                 _MAX_POLLS, _stream_ptr())
-        if status != 0:
-            raise RuntimeError(f"w4a16_wait_peers failed: {_native.status_string(status)}")
+    def _counter(self, index: int) -> int:
+        return self.counters.data_ptr() + 4 * index
+
+    def out_table(self, byte_offset: int) -> torch.Tensor:
+        """Device array of every rank's result buffer 0 plus ``byte_offset``."""
+        if byte_offset not in self._tables:
+            self._tables[byte_offset] = torch.tensor([p + byte_offset for p in self.peer_base], dtype=torch.int64,
+                                                     device=self.buffer.device)
+        return self._tables[byte_offset]
+
+    def target(self, byte_offset: int, ld: int, column_offset: int) -> _native.PeerTarget:
+        return _native.PeerTarget(self.out_table(byte_offset).data_ptr(), self._published_table.data_ptr(),
+                                  self.base + 2 * self.result_bytes + 256, self._counter(0), self._counter(1),
+                                  self._counter(3), self.result_bytes, ld, column_offset, self.max_polls, self.rank,
+                                  self.world)
+
+    def source(self) -> _native.PeerSource:
+        return _native.PeerSource(self._counter(1), self.base + 2 * self.result_bytes, self._consumed_table.data_ptr(),
+                                  self._counter(2), self._counter(3), self.result_bytes, self.max_polls, self.rank,
+                                  self.world)
 
     def check(self) -> None:
-        """Host-side health check (synchronises): raises if a wait gave up on some rank."""
-        missing = int(self.counters[3].item())
-        if missing:
-            raise RuntimeError(f"rank {missing - 1} never published its part of a sharded layer")
+        """Host-side health check (synchronises): raises if a bounded wait gave up on some rank."""
+        code = int(self.counters[3].item())
+        if code > 32:
+            raise RuntimeError(f"rank {code - 33} never released a result buffer of a sharded layer")
+        if code:
+            raise RuntimeError(f"rank {code - 1} never published its part of a sharded layer")
+
+
+class PeerView:
+    """The gathered ``[rows, columns]`` FP16 result of a peer layer's latest launch, still in its result
+    buffer and possibly still arriving.  Hand it to another peer layer's ``launch`` (that kernel then does the
+    waiting, in its prologue) or call ``materialize()`` (a small kernel waits and copies it out).  Every
+    launch's view must be consumed exactly once on every rank before the layer is launched a third time."""
+
+    def __init__(self, region: PeerRegion, rows: int, ld: int, column0: int = 0, columns: int | None = None):
+        self.region, self.rows, self.ld, self.column0 = region, rows, ld, column0
+        self.columns = ld if columns is None else columns
+
+    def narrow(self, column0: int, columns: int) -> "PeerView":
+        if column0 < 0 or column0 + columns > self.columns or column0 % 8:
+            raise ValueError("column slice out of range or not a multiple of 8")
+        return PeerView(self.region, self.rows, self.ld, self.column0 + column0, columns)
+
+    @property
+    def data_ptr(self) -> int:
+        return self.region.base + 2 * self.column0
+
+    def materialize(self) -> torch.Tensor:
+        if self.column0 or self.columns != self.ld:
+            raise ValueError("materialize() copies whole rows: call it on the un-narrowed view")
+        if (self.rows * self.ld) % 8:
+            raise ValueError("rows * columns must be a multiple of 8")
+        out = torch.empty((self.rows, self.ld), dtype=torch.float16, device=self.region.buffer.device)
+        source = self.region.source()
+        status = _native.core().w4a16_wait_peers(ctypes.byref(source), self.region.base, out.data_ptr(),
+                                                 out.numel() * 2, _launch_flags(), _stream_ptr())
+        if status != 0:
+            raise RuntimeError(f"w4a16_wait_peers failed: {_native.status_string(status)}")
+        return out
 
 
 def _workspace(m: int, n: int, k: int, device) -> torch.Tensor | None:
@@ -196,98 +282,125 @@ def _workspace(m: int, n: int, k: int, device) -> torch.Tensor | None:
     return torch.zeros(need, dtype=torch.uint8, device=device) if need else None
 
 
-class PeerColumnParallelQuantizedLinear(torch.nn.Module):
-    """Column-parallel layer whose all-gather is the kernel's own epilogue.
+def _launch_peer_linear(layer: QuantizedLinear, x, m: int, workspaces: dict, target, out_f32: bool, y=None) -> None:
+    """One fused linear whose input is a tensor or a ``PeerView`` and whose output goes to ``target`` (or ``y``)."""
+    if isinstance(x, PeerView):
+        if x.columns != layer.in_features or x.rows != m:
+            raise ValueError("the view's shape does not match the layer")
+        x_ptr, x_ld, source = x.data_ptr, x.ld, x.region.source()
+        device = x.region.buffer.device
+    else:
+        if x.dtype != torch.float16 or x.ndim != 2 or x.shape[1] != layer.in_features or x.stride(1) != 1:
+            raise ValueError("activations must be FP16 [M, K] with unit stride along K")
+        _require_cuda(x)
+        x_ptr, x_ld, source, device = x.data_ptr(), x.stride(0) if m > 1 else layer.in_features, None, x.device
+    if m not in workspaces:
+        workspaces[m] = _workspace(m, layer.out_features, layer.in_features, device)
+    ws = workspaces[m]
+    flags = _launch_flags() | (_native.FLAG_OUTPUT_F32 if out_f32 else 0)
+    status = _native.core().w4a16_linear_f16_peers(
+        x_ptr, x_ld, layer.packed_weights.data_ptr(), layer.scales.data_ptr(), None if y is None else y.data_ptr(), m,
+        layer.out_features, layer.in_features, 128, ws.data_ptr() if ws is not None else None,
+        ws.numel() if ws is not None else 0, flags, None if target is None else ctypes.byref(target),
+        None if source is None else ctypes.byref(source), _stream_ptr())
+    if status != 0:
+        raise RuntimeError(f"w4a16_linear_f16_peers failed: {_native.status_string(status)}")
 
-    Every rank's kernel stores its ``[M, N/G]`` slice into the ``[M, N]`` result buffer of every
-    rank and then raises a flag there; ``forward`` returns this rank's buffer after a bounded wait
-    for all flags.  ``max_rows`` fixes the largest batch the buffers are sized for.  The returned
-    tensor is reused by the next call of this layer.
+
+class PeerColumnParallelQuantizedLinear(torch.nn.Module):
+    """Column-parallel layer whose all-gather is done by the kernels themselves.
+
+    ``launch(x)`` runs this rank's slice and stores the ``[M, N/G]`` result into the ``[M, N]`` result buffer
+    of every rank; it returns a ``PeerView`` and does not wait.  ``forward(x)`` is ``launch(x).materialize()``.
+    ``x`` may itself be a ``PeerView`` (of a column slice) of another peer layer.  ``max_rows`` fixes the
+    largest batch the buffers are sized for.
     """
 
-    def __init__(self, packed_shard, scales_shard, group_size=128, process_group=None, max_rows=8):
+    def __init__(self, packed_shard, scales_shard, group_size=128, process_group=None, max_rows=8, *,
+                 local: LocalRanks | None = None, rank: int | None = None, name: str | None = None,
+                 max_polls: int = _MAX_POLLS):
         super().__init__()
+        if local is not None and (rank is None or name is None):
+            raise ValueError("with LocalRanks, give this rank's index and a name shared by the layer's ranks")
         if group_size != 128:
             raise ValueError("the peer-store path needs group_size == 128")
         self.local = QuantizedLinear(packed_shard, scales_shard, group_size)
         n_local = self.local.out_features
-        self.region = _PeerRegion(max_rows * n_local * dist.get_world_size(process_group) * 2, process_group)
+        world = local.world if local is not None else dist.get_world_size(process_group)
+        self.region = PeerRegion(max_rows * n_local * world * 2, process_group, local=local, rank=rank, key=name,
+                                 max_polls=max_polls)
         self.max_rows = max_rows
+        self.in_features = self.local.in_features
         self.out_features = n_local * self.region.world
-        self._out_table = self.region.table(lambda r: 0)
-        self._workspace = {}
+        self._workspace: dict = {}
+
+    def launch(self, x) -> PeerView:
+        m = x.rows if isinstance(x, PeerView) else x.shape[0]
+        if m > self.max_rows:
+            raise ValueError(f"batch of {m} rows exceeds max_rows={self.max_rows}")
+        region = self.region
+        target = region.target(0, self.out_features, region.rank * self.local.out_features)
+        _launch_peer_linear(self.local, x, m, self._workspace, target, out_f32=False)
+        return PeerView(region, m, self.out_features)
 
     def forward(self, activations: torch.Tensor) -> torch.Tensor:
-        layer, region = self.local, self.region
         if activations.dtype != torch.float16:
             raise TypeError("activations must have dtype torch.float16")
         _require_cuda(activations)
-        flat = activations.contiguous().reshape(-1, layer.in_features)
-        m = flat.shape[0]
-        if m > self.max_rows:
-            raise ValueError(f"batch of {m} rows exceeds max_rows={self.max_rows}")
-        if m not in self._workspace:
-            self._workspace[m] = _workspace(m, layer.out_features, layer.in_features, flat.device)
-        ws = self._workspace[m]
-        # wait=True: the launch returns to the stream only when every rank's slice has landed here
-        target = region.target(self._out_table, self.out_features, region.rank * layer.out_features, wait=True)
-        flags = _native.FLAG_PROGRAMMATIC_LAUNCH if _cuda.programmatic_launch_enabled() else 0
-        status = _native.core().w4a16_linear_f16_peers(
-            flat.data_ptr(), layer.packed_weights.data_ptr(), layer.scales.data_ptr(), m, layer.out_features,
-            layer.in_features, 128, ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
-            flags, ctypes.byref(target), _stream_ptr())
-        if status != 0:
-            raise RuntimeError(f"w4a16_linear_f16_peers failed: {_native.status_string(status)}")
-        full = region.buffer[: m * self.out_features * 2].view(torch.float16).view(m, self.out_features)
-        return full.reshape(*activations.shape[:-1], self.out_features)
+        flat = activations.contiguous().reshape(-1, self.in_features)
+        return self.launch(flat).materialize().reshape(*activations.shape[:-1], self.out_features)
 
 
 class PeerRowParallelQuantizedLinear(torch.nn.Module):
     """Row-parallel layer (K split) with a one-shot all-reduce built from peer stores.
 
-    Each rank's kernel writes its FP32 partial ``[M, N]`` into slot ``rank`` of the staging buffer on
-    every rank and raises a flag; after a bounded wait each rank sums the ``G`` partials in rank order
-    (identical bits everywhere) and rounds once to FP16.  Takes this rank's K-slice of x.
+    ``launch(x)``: this rank's kernel writes its FP32 partial ``[M, N]`` into slot ``rank`` of the staging
+    buffer on every rank and raises a flag.  ``finish(m)``: one small kernel waits (bounded) for every rank's
+    partial, sums the ``G`` partials in rank order (identical bits everywhere), rounds once to FP16 and gives the
+    staging buffer back.  ``forward`` is both.  Takes this rank's K-slice of x (a tensor or a ``PeerView``).
     """
 
-    def __init__(self, packed_shard, scales_shard, group_size=128, process_group=None, max_rows=8):
+    def __init__(self, packed_shard, scales_shard, group_size=128, process_group=None, max_rows=8, *,
+                 local: LocalRanks | None = None, rank: int | None = None, name: str | None = None,
+                 max_polls: int = _MAX_POLLS):
         super().__init__()
+        if local is not None and (rank is None or name is None):
+            raise ValueError("with LocalRanks, give this rank's index and a name shared by the layer's ranks")
         if group_size != 128:
             raise ValueError("the peer-store path needs group_size == 128")
         self.local = QuantizedLinear(packed_shard, scales_shard, group_size)
-        world = dist.get_world_size(process_group)
-        self.region = _PeerRegion(world * max_rows * self.local.out_features * 4, process_group)
+        world = local.world if local is not None else dist.get_world_size(process_group)
+        n = self.local.out_features
+        self.region = PeerRegion(world * max_rows * n * 4, process_group, local=local, rank=rank, key=name,
+                                 max_polls=max_polls)
         self.max_rows = max_rows
-        self._tables = {}
-        self._workspace = {}
+        self.in_features = self.local.in_features
+        self.out_features = n
+        self._workspace: dict = {}
+
+    def launch(self, x) -> int:
+        m = x.rows if isinstance(x, PeerView) else x.shape[0]
+        if m > self.max_rows:
+            raise ValueError(f"batch of {m} rows exceeds max_rows={self.max_rows}")
+        region, n = self.region, self.out_features
+        target = region.target(region.rank * m * n * 4, n, 0)   # my slot on every rank
+        _launch_peer_linear(self.local, x, m, self._workspace, target, out_f32=True)
+        return m
+
+    def finish(self, m: int, out: torch.Tensor | None = None) -> torch.Tensor:
+        region, n = self.region, self.out_features
+        if out is None:
+            out = torch.empty((m, n), dtype=torch.float16, device=region.buffer.device)
+        source = region.source()
+        status = _native.core().w4a16_sum_partials_f16(region.base, out.data_ptr(), m * n, region.world,
+                                                       ctypes.byref(source), _launch_flags(), _stream_ptr())
+        if status != 0:
+            raise RuntimeError(f"w4a16_sum_partials_f16 failed: {_native.status_string(status)}")
+        return out
 
     def forward(self, activations: torch.Tensor) -> torch.Tensor:
-        layer, region = self.local, self.region
         if activations.dtype != torch.float16:
             raise TypeError("activations must have dtype torch.float16")
         _require_cuda(activations)
-        flat = activations.contiguous().reshape(-1, layer.in_features)
-        m, n = flat.shape[0], layer.out_features
-        if m > self.max_rows:
-            raise ValueError(f"batch of {m} rows exceeds max_rows={self.max_rows}")
-        if m not in self._tables:
-            self._tables[m] = region.table(lambda r: region.rank * m * n * 4)   # my slot on every rank
-            self._workspace[m] = _workspace(m, n, layer.in_features, flat.device)
-        ws = self._workspace[m]
-        target = region.target(self._tables[m], n, 0, wait=False)   # the summing kernel does the waiting
-        flags = _native.FLAG_OUTPUT_F32 | (_native.FLAG_PROGRAMMATIC_LAUNCH if _cuda.programmatic_launch_enabled() else 0)
-        lib = _native.core()
-        status = lib.w4a16_linear_f16_peers(
-            flat.data_ptr(), layer.packed_weights.data_ptr(), layer.scales.data_ptr(), m, n, layer.in_features, 128,
-            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, flags,
-            ctypes.byref(target), _stream_ptr())
-        if status != 0:
-            raise RuntimeError(f"w4a16_linear_f16_peers failed: {_native.status_string(status)}")
-        out = torch.empty((m, n), dtype=torch.float16, device=flat.device)
-        counters = region.counters.data_ptr()
-        status = lib.w4a16_sum_partials_f16(region.buffer.data_ptr(), out.data_ptr(), m * n, region.world,
-                                            region.buffer.data_ptr() + region.result_bytes, counters + 4, counters + 12,
-                                            _MAX_POLLS, _stream_ptr())
-        if status != 0:
-            raise RuntimeError(f"w4a16_sum_partials_f16 failed: {_native.status_string(status)}")
-        return out.reshape(*activations.shape[:-1], n)
+        flat = activations.contiguous().reshape(-1, self.in_features)
+        return self.finish(self.launch(flat)).reshape(*activations.shape[:-1], self.out_features)

@@ -16,6 +16,10 @@ Fixtures written:
                       SHA-256 digests of the packed codes and scales (inputs are
                       re-derived from the seeds by the tests)
   config1_m8.npz      K=N=2048 at M=8, same seeds
+  tinyllama_small_batch.npz
+                      the five TinyLlama-shaped layers at M = 2, 4 and 8 (the small-batch sweep of
+                      the reference's tests/test_cuda.py:397-451, at full size): reference outputs
+                      only; lm_head outputs are kept for a fixed column sample to bound the file
 """
 from __future__ import annotations
 
@@ -47,6 +51,13 @@ def seeded_weights(n: int, k: int, seed: int = 0) -> torch.Tensor:
 def seeded_activations(m: int, k: int, seed: int = 1) -> torch.Tensor:
     g = torch.Generator().manual_seed(seed)
     return torch.randn((m, k), dtype=torch.float32, generator=g).half()
+
+
+def small_batch_columns(n: int) -> np.ndarray:
+    """Output columns kept in tinyllama_small_batch.npz: all of them up to 8192, else both ends and every 16th."""
+    if n <= 8192:
+        return np.arange(n, dtype=np.int64)
+    return np.unique(np.concatenate([np.arange(256), np.arange(0, n, 16), np.arange(n - 256, n)])).astype(np.int64)
 
 
 def sha(t: torch.Tensor) -> str:
@@ -131,6 +142,19 @@ def main(reference_root: str) -> None:
         x=x.numpy(),
         y=ref.linear_reference(x, packed, scales, 128).numpy(),
     )
+    # ---- the small-batch sweep: every TinyLlama-shaped layer at M = 2, 4, 8 -----------
+    batch = {}
+    for index, (name, k, n) in enumerate(TINYLLAMA_LAYERS):
+        w = seeded_weights(n, k, seed=index)
+        packed, scales = quant.quantize_and_pack_weights(w, 128)
+        columns = small_batch_columns(n)
+        batch[f"{name}/columns"] = columns
+        for m in (2, 4, 8):
+            x = seeded_activations(m, k, seed=2000 + 10 * index + m)
+            y = ref.linear_reference(x, packed, scales, 128).numpy()
+            batch[f"{name}/m{m}/x_sha256"] = np.array(sha(x))
+            batch[f"{name}/m{m}/y"] = y[:, columns]
+    np.savez_compressed(HERE / "tinyllama_small_batch.npz", **batch)
     print("golden fixtures written to", HERE)
 
 

@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_version_and_status_strings():
     lib = _native.core()
-    assert lib.w4a16_abi_version() == 1
+    assert lib.w4a16_abi_version() == 2
     assert _native.status_string(0) == "ok"
     for code in range(-8, 0):
         assert _native.status_string(code) not in ("ok", "unknown status")
@@ -71,6 +71,13 @@ def test_workspace_size_query():
     # a tall-K, few-rows problem asks for split-K scratch; a wide one does not
     assert lib.w4a16_linear_workspace_bytes(1, 1024, 8192) > 0
     assert lib.w4a16_linear_workspace_bytes(1, 32000, 2048) == 0
+    # prefill-sized batches run the tcgen05 GEMM, which has no scratch -- unless a flag keeps them off it
+    assert lib.w4a16_linear_workspace_bytes(512, 8192, 8192) == 0
+    assert lib.w4a16_linear_workspace_bytes_flags(512, 8192, 8192, 0) == 0
+    assert lib.w4a16_linear_workspace_bytes_flags(512, 8192, 8192, _native.FLAG_NO_TCGEN05) > 0
+    assert lib.w4a16_linear_workspace_bytes_flags(512, 8192, 8192, _native.FLAG_OUTPUT_F32) > 0
+    assert lib.w4a16_linear_workspace_bytes_flags(1, 1024, 8192, _native.FLAG_FORCE_GENERIC) == 0
+    assert lib.w4a16_linear_workspace_bytes_flags(32, 8192, 8192, 0) == lib.w4a16_linear_workspace_bytes(32, 8192, 8192) > 4 << 20
 
 
 def test_missing_library_is_an_error(monkeypatch, tmp_path):

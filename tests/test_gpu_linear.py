@@ -46,6 +46,23 @@ def test_config1_m8_against_reference_outputs(golden):
     check_against_oracle(y, x, packed, scales)
 
 
+@pytest.mark.parametrize("m", [2, 4, 8])
+@pytest.mark.parametrize(("name", "k", "n"), TINYLLAMA_LAYERS)
+def test_tinyllama_layers_small_batch_against_reference_outputs(golden, name, k, n, m):
+    """The small-batch sweep at full size: M in {2, 4, 8} over all five TinyLlama-shaped layers, against
+    outputs of the reference's CPU path on the same seeds (reference cases tests/test_cuda.py:397-451)."""
+    data = golden("tinyllama_small_batch.npz")
+    index = [layer[0] for layer in TINYLLAMA_LAYERS].index(name)
+    packed, scales = quantize_and_pack_weights(seeded_weights(n, k, seed=index), 128)
+    x = seeded_activations(m, k, seed=2000 + 10 * index + m)
+    y = capi_linear(x.cuda(), packed.cuda(), scales.cuda())
+    columns = torch.from_numpy(data[f"{name}/columns"])
+    torch.testing.assert_close(y.cpu()[:, columns], torch.from_numpy(data[f"{name}/m{m}/y"]), rtol=1e-2, atol=1e-2)
+    rows = None if n <= 8192 else data[f"{name}/columns"]
+    check_against_oracle(y, x, packed, scales, rows=rows)
+    assert torch.equal(linear_cuda(x.cuda(), packed.cuda(), scales.cuda(), 128), y)
+
+
 @pytest.mark.parametrize("tag", ["n8_k256_g128_m4", "n7_k256_g128_m1", "n13_k384_g64_m3", "n16_k128_g32_m2",
                                  "n5_k64_g4_m9", "n33_k1024_g128_m8"])
 def test_small_golden_cases(golden, tag):

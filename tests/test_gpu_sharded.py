@@ -45,7 +45,9 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
                 got = layer(x.cuda()).cpu().numpy().astype(np.float64)
                 assert got.shape == (m, n)
                 assert (np.abs(got - exact) <= bound).all(), type(layer).__name__
-        # the same two cuts with the exchange done by the kernel epilogue (peer stores + flags)
+        # the same two cuts with the exchange done by the kernels themselves (peer stores + flags); calls follow
+        # each other without any barrier between them: the two result buffers and the release flags keep a
+        # fast rank from overwriting what a slow rank still reads
         from nibble_b200.sharded import (PeerColumnParallelQuantizedLinear, PeerRowParallelQuantizedLinear, shard_k,
                                          shard_rows)
 
@@ -53,19 +55,49 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         p_k, s_k = shard_k(packed.cuda(), scales.cuda(), rank, world, 128)
         peer_col = PeerColumnParallelQuantizedLinear(p_rows, s_rows, 128, max_rows=8)
         peer_row = PeerRowParallelQuantizedLinear(p_k, s_k, 128, max_rows=8)
-        for repeat in range(3):          # epochs advance; buffers and flags are reused
+        results = []
+        for repeat in range(4):          # publication numbers advance; buffers and flags are reused
             for m in (1, 8, 3):
                 x = torch.randn((m, k), generator=g).half()
-                exact = oracle.linear_fp64(x.numpy(), packed.numpy(), scales.numpy(), 128)
-                bound = oracle.error_bound(x.numpy(), packed.numpy(), scales.numpy(), 128)
-                got = peer_col(x.cuda()).float().cpu().numpy().astype(np.float64)
-                assert got.shape == (m, n) and (np.abs(got - exact) <= bound).all(), ("peer column", repeat, m)
                 x_mine = x[:, rank * k // world:(rank + 1) * k // world].contiguous()
-                got = peer_row(x_mine.cuda()).float().cpu().numpy().astype(np.float64)
-                assert got.shape == (m, n) and (np.abs(got - exact) <= bound).all(), ("peer row", repeat, m)
-                dist.barrier()           # nobody overwrites a buffer a slower rank is still reading
+                if rank == 1 and repeat == 1:
+                    torch.cuda._sleep(20_000_000)      # a slow rank: the other one runs ahead as far as the protocol lets it
+                results.append((x, peer_col(x.cuda()), peer_row(x_mine.cuda())))
+        torch.cuda.synchronize()
+        for x, got_col, got_row in results:
+            exact = oracle.linear_fp64(x.numpy(), packed.numpy(), scales.numpy(), 128)
+            bound = oracle.error_bound(x.numpy(), packed.numpy(), scales.numpy(), 128)
+            for name, got in (("peer column", got_col), ("peer row", got_row)):
+                got = got.float().cpu().numpy().astype(np.float64)
+                assert got.shape == exact.shape and (np.abs(got - exact) <= bound).all(), name
         peer_col.region.check()
         peer_row.region.check()
+
+        # a chain: column-parallel -> column-parallel reading the first one's result in its own prologue ->
+        # row-parallel reading a column slice -> sum; twelve steps back to back
+        g2 = torch.Generator().manual_seed(5)
+        w_a = quantize_and_pack_weights(torch.randn((512, 1024), generator=g2) * 0.05, 128)
+        w_b = quantize_and_pack_weights(torch.randn((1024, 512), generator=g2) * 0.05, 128)
+        w_c = quantize_and_pack_weights(torch.randn((256, 1024), generator=g2) * 0.05, 128)
+        col_a = PeerColumnParallelQuantizedLinear(*shard_rows(w_a[0].cuda(), w_a[1].cuda(), rank, world), 128, max_rows=8)
+        col_b = PeerColumnParallelQuantizedLinear(*shard_rows(w_b[0].cuda(), w_b[1].cuda(), rank, world), 128, max_rows=8)
+        row_c = PeerRowParallelQuantizedLinear(*shard_k(w_c[0].cuda(), w_c[1].cuda(), rank, world, 128), 128, max_rows=8)
+        k_local = 1024 // world
+        chained = []
+        for step in range(12):
+            m = (1, 8, 4)[step % 3]
+            x = torch.randn((m, 1024), generator=g2).half()
+            view_b = col_b.launch(col_a.launch(x.cuda()))
+            row_c.launch(view_b.narrow(rank * k_local, k_local))
+            chained.append((x, row_c.finish(m)))
+        torch.cuda.synchronize()
+        for x, got in chained:
+            a = oracle.linear_reference(x.numpy(), w_a[0].numpy(), w_a[1].numpy(), 128)
+            b = oracle.linear_reference(a, w_b[0].numpy(), w_b[1].numpy(), 128)
+            c = oracle.linear_reference(b, w_c[0].numpy(), w_c[1].numpy(), 128)
+            torch.testing.assert_close(got.cpu(), torch.from_numpy(c), rtol=3e-2, atol=3e-2)
+        for layer in (col_a, col_b, row_c):
+            layer.region.check()
         torch.cuda.synchronize()
         dist.barrier()
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()

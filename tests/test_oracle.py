@@ -136,9 +136,28 @@ def test_config1_m1_full_size(golden):
     assert (err <= oracle.error_bound(x, packed, scales, 128)).all()
 
 
+@pytest.mark.parametrize("name", ["qo_proj", "kv_proj", "gate_up_proj", "down_proj"])
+def test_small_batch_sweep_full_size(golden, name):
+    """M = 2, 4, 8 on the full-size TinyLlama-shaped layers (the small-batch sweep), from the seeds."""
+    from conftest import TINYLLAMA_LAYERS, seeded_activations, seeded_weights
+
+    data = golden("tinyllama_small_batch.npz")
+    index = [layer[0] for layer in TINYLLAMA_LAYERS].index(name)
+    _, k, n = TINYLLAMA_LAYERS[index]
+    packed, scales = oracle.quantize_and_pack_weights(seeded_weights(n, k, seed=index).numpy(), 128)
+    columns = data[f"{name}/columns"]
+    for m in (2, 4, 8):
+        x = seeded_activations(m, k, seed=2000 + 10 * index + m).numpy()
+        assert hashlib.sha256(x.tobytes()).hexdigest() == str(data[f"{name}/m{m}/x_sha256"])
+        y = oracle.linear_reference(x, packed, scales, 128)
+        _assert_within_one_half_ulp_step(np.ascontiguousarray(y[:, columns]), data[f"{name}/m{m}/y"])
+
+
 def _assert_within_one_half_ulp_step(mine: np.ndarray, theirs: np.ndarray) -> None:
     """Both sides round an FP32 matmul to FP16; BLAS summation order may move a value
-    sitting on a rounding boundary by one FP16 step, never more."""
+    sitting on a rounding boundary by one FP16 step, never more -- except for outputs that cancel
+    to almost nothing, where the FP32 summation noise itself (a few 1e-6 on sums of terms of order
+    0.1) spans several of the much finer FP16 steps near zero."""
     assert mine.shape == theirs.shape and mine.dtype == theirs.dtype == np.float16
     a = mine.view(np.int16).astype(np.int32)
     b = theirs.view(np.int16).astype(np.int32)
@@ -146,7 +165,8 @@ def _assert_within_one_half_ulp_step(mine: np.ndarray, theirs: np.ndarray) -> No
     a = np.where(a < 0, -(a & 0x7FFF), a)
     b = np.where(b < 0, -(b & 0x7FFF), b)
     steps = np.abs(a - b)
-    assert steps.max(initial=0) <= 1, f"max FP16 step distance {steps.max()}"
+    noise = np.abs(mine.astype(np.float32) - theirs.astype(np.float32)) <= 4e-6
+    assert np.where(noise, 0, steps).max(initial=0) <= 1, f"max FP16 step distance {steps.max()}"
     assert (steps > 0).mean() < 0.02
 
 

@@ -61,6 +61,28 @@ def test_matches_the_workspace_entry_point_twice_in_a_row(m, n, k):
     check_against_oracle(second, x, packed, scales, rows=rows)
 
 
+@pytest.mark.parametrize(("m", "n", "k"), [(128, 5632, 2048), (512, 8192, 8192), (65, 300, 1024)])
+def test_batches_that_need_no_scratch_are_forwarded(m, n, k):
+    """From 65 rows on the ordinary entry point runs the tcgen05 GEMM, which has no split-K scratch, so the
+    allocation-free entry point must run such batches too, whatever their size, and give the same bits."""
+    lib = _native.core()
+    assert lib.w4a16_linear_workspace_bytes_flags(m, n, k, 0) == 0
+    assert lib.w4a16_linear_workspace_bytes_flags(m, n, k, _native.FLAG_NO_TCGEN05) > 0 or n == 300
+    torch.manual_seed(m + n)
+    packed = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda")
+    scales = (torch.rand((n, k // 128), device="cuda") * 0.01 + 1e-3).half()
+    x = torch.randn((m, k), device="cuda").half()
+    expected = capi_linear(x, packed, scales)
+    first = _static_scratch_linear(x, packed, scales)
+    second = _static_scratch_linear(x, packed, scales)
+    torch.cuda.synchronize()
+    assert torch.equal(first, expected) and torch.equal(second, expected)
+    rows = list(range(0, n, max(1, n // 64)))
+    check_against_oracle(second[:32].contiguous(), x[:32].contiguous(), packed, scales, rows=rows, fp16_weights=True)
+    value = ctypes.c_uint32(7)
+    assert lib.w4a16_device_status(ctypes.byref(value)) == 0 and value.value == 0
+
+
 def test_scratch_size_is_reported_and_oversized_problems_are_refused():
     lib = _native.core()
     capacity = lib.w4a16_static_scratch_bytes()
