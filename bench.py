@@ -21,7 +21,7 @@ scripts/profile_kernel.py:310-323).
   run under the kernels of step i; ``one_stream_*`` is the same work serialised on one stream.
 * ``roofline`` -- the fused kernel's bytes per launch over its mean launch duration inside the
   timed region, against the measured HBM copy bandwidth.
-* ``cpu_baseline`` -- the CPU restatement of the reference's PyTorch path on the host cores.
+* ``cpu_baseline`` -- the reference's PyTorch CPU path on the host cores (the reference arm as a child process).
 * ``layers`` -- per-shape latency of isolated launches over rotating weight copies (> 2x L2 per
   graph replay), M=1, 2, 4 and 8, next to cuBLAS FP16 on the dequantised weights.
 * ``fused_siblings``, ``prefill``, ``quantize``, ``decode`` -- the token with q/k/v and gate/up as
@@ -36,7 +36,8 @@ the N GPUs -- column-parallel q/k/v, o, gate/up and row-parallel down -- at M = 
 exchange done by the kernels themselves, by NCCL, with the two-exchange pairing, without any exchange,
 and unsharded on one GPU (``sharded_block_bench``).
 
-``--impl reference`` times the CPU restatement alone, one decoder block per step.
+``--impl reference`` times the reference's own CPU code (``oracle/_ref``, built by oracle/build_ref.py where a
+checkout of the reference exists; else the restatement in oracle/torch_cpu_port.py), one decoder block per step.
 """
 from __future__ import annotations
 
@@ -310,34 +311,19 @@ def quantize_table(torch, device) -> dict:
     return out
 
 
-def cpu_pass(torch, layers, sample_name: str, repeats: int) -> dict:
-    """Times the CPU restatement on `layers` (list of (name, K, N)); returns GB/s over the sample."""
-    from nibble_b200 import quantize_and_pack_weights
-    from oracle import torch_cpu_port as port
+def cpu_baseline_leg(blocks: int, repeats: int) -> dict:
+    """The CPU baseline of the product line: this script's own reference arm, run as a child process (so that
+    the reference's modules are imported in an interpreter that has not loaded this package) on a bounded
+    sample of the workload -- `blocks` decoder blocks per pass, `repeats` timed passes."""
+    import subprocess
 
-    torch.set_num_threads(os.cpu_count() or 1)
-    data = []
-    for index, (_, k, n) in enumerate(layers):
-        g = torch.Generator().manual_seed(index)
-        w = torch.randn((n, k), dtype=torch.float32, generator=g) * 0.02
-        packed, scales = quantize_and_pack_weights(w, GROUP)
-        x = torch.randn((1, k), dtype=torch.float32, generator=g).half()
-        data.append((x, packed, scales))
-    total_bytes = sum(algorithmic_bytes(1, k, n) for _, k, n in layers)
-
-    def one_pass():
-        for x, packed, scales in data:
-            port.linear(x, packed, scales, GROUP)
-
-    one_pass()
-    times = []
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        one_pass()
-        times.append(time.perf_counter() - t0)
-    seconds = statistics.median(times)
-    return {"value": round(total_bytes / seconds / 1e9, 3), "unit": "GB/s", "cores": torch.get_num_threads(),
-            "kind": "port", "sample": sample_name, "seconds_per_sample": round(seconds, 4)}
+    cmd = [sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", str(repeats), "--warmup", "3",
+           "--cpu-blocks", str(blocks)]
+    env = {key: value for key, value in os.environ.items() if key not in ("RANK", "LOCAL_RANK", "WORLD_SIZE")}
+    proc = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    if proc.returncode != 0 or not proc.stdout.strip():
+        return {"value": None, "unit": "GB/s", "cores": None, "kind": "unavailable", "sample": proc.stderr[-300:]}
+    return json.loads(proc.stdout.strip().splitlines()[-1])["cpu_baseline"]
 
 
 def decode_bench(torch, device) -> dict:
@@ -1126,8 +1112,7 @@ def run_product(args) -> dict:
         except Exception as error:   # transformers API drift must not cost the headline line
             result["decode"] = {"error": repr(error)[:300]}
     if rank == 0 and world == 1:
-        block = [(name, *TINYLLAMA[name]) for name in BLOCK_ORDER]
-        result["cpu_baseline"] = cpu_pass(torch, block * 4, "4 decoder blocks (28 linears) of the workload, M=1", repeats=5)
+        result["cpu_baseline"] = cpu_baseline_leg(blocks=4, repeats=5)
     if world > 1:
         # the layers that ARE worth sharding: one Llama-3-70B-shaped decoder block over this job's GPUs
         del graph
@@ -1145,44 +1130,74 @@ def run_product(args) -> dict:
 
 # ----------------------------------------------------------------------------- reference arm
 def run_reference(args) -> dict:
-    """The reference's CPU path (restated in oracle/torch_cpu_port.py) on the host cores."""
+    """The reference's own CPU implementation of the path on the host cores, all threads.
+
+    Where ``oracle/_ref`` holds the reference's compiled modules (oracle/build_ref.py) those are what runs:
+    ``w4a16.quantization.quantize_and_pack_weights`` makes the packed weights and ``w4a16.reference.linear_reference``
+    is timed (kind "reference").  Otherwise the restatement in oracle/torch_cpu_port.py is timed (kind "port").
+    Nothing of this package is imported either way.  One step = `--cpu-blocks` decoder blocks of the workload.
+    """
     if int(os.environ.get("RANK", "0")) != 0:
         return {}
+    ref_root = ROOT / "oracle" / "_ref"
+    use_ref = all((ref_root / "w4a16" / name).is_file() for name in ("__init__.py", "quantization.pyc", "reference.pyc"))
+    if use_ref:
+        sys.path.insert(0, str(ref_root))
     import torch
 
-    block = [(name, *TINYLLAMA[name]) for name in BLOCK_ORDER]
-    from nibble_b200 import quantize_and_pack_weights
-    from oracle import torch_cpu_port as port
-
     torch.set_num_threads(os.cpu_count() or 1)
+    if use_ref:
+        from w4a16 import quantization as ref_quant, reference as ref_linear   # the reference's modules
+
+        assert pathlib.Path(ref_linear.__file__).resolve().is_relative_to(ref_root.resolve())
+        kind = "reference"
+
+        def quantise(w):
+            return ref_quant.quantize_and_pack_weights(w, GROUP)
+
+        linear = ref_linear.linear_reference
+    else:
+        from oracle import torch_cpu_port as port, w4a16_oracle as oracle
+
+        kind = "port"
+
+        def quantise(w):
+            packed, scales = oracle.quantize_and_pack_weights(w.numpy(), GROUP)
+            return torch.from_numpy(packed), torch.from_numpy(scales)
+
+        linear = port.linear
+    block = [(name, *TINYLLAMA[name]) for name in BLOCK_ORDER] * max(1, args.cpu_blocks)
     data = []
     for index, (_, k, n) in enumerate(block):
         g = torch.Generator().manual_seed(index)
-        packed, scales = quantize_and_pack_weights(torch.randn((n, k), generator=g) * 0.02, GROUP)
+        packed, scales = quantise(torch.randn((n, k), generator=g) * 0.02)
         data.append((torch.randn((1, k), generator=g).half(), packed, scales))
     step_bytes = sum(algorithmic_bytes(1, k, n) for _, k, n in block)
 
     def step():
         for x, packed, scales in data:
-            port.linear(x, packed, scales, GROUP)
+            linear(x, packed, scales, GROUP)
 
     warmup = max(args.warmup, 3)
     for _ in range(warmup):
         step()
-    t0 = time.perf_counter()
+    times = []
     for _ in range(args.steps):
+        t0 = time.perf_counter()
         step()
-    ms_per_step = (time.perf_counter() - t0) * 1e3 / args.steps
+        times.append(time.perf_counter() - t0)
+    ms_per_step = sum(times) * 1e3 / args.steps
     value = step_bytes / (ms_per_step * 1e-3) / 1e9
-    sample = "one decoder block (7 linears, 22.8 MB) per step on the host cores"
+    sample = (f"{max(1, args.cpu_blocks)} decoder block(s) of the workload ({len(block)} linears, "
+              f"{step_bytes / 1e6:.1f} MB) per step, M=1, on the host cores")
     return {
         "impl": "reference", "metric": "w4a16_linear_hbm_gbs_m1", "value": round(value, 3), "unit": "GB/s",
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms_per_step, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32 (torch CPU)", "data": "synthetic (seeded N(0,0.02) weights, N(0,1) activations)",
         "config": {"workload": "tinyllama_decode_linears_m1", "M": 1, "group_size": GROUP, "sample": sample},
-        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": sample},
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": torch.get_num_threads(), "kind": kind,
+                         "sample": sample, "seconds_per_sample": round(statistics.median(times), 4)},
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -1203,6 +1218,8 @@ def main() -> None:
     parser.add_argument("--workload", choices=["tinyllama_decode_linears_m1", "llama70b_tp", "decode_step"],
                         default="tinyllama_decode_linears_m1")
     parser.add_argument("--batch", type=int, default=1, help="M for --workload llama70b_tp")
+    parser.add_argument("--cpu-blocks", type=int, default=1,
+                        help="--impl reference: decoder blocks (7 linears each) per step")
     parser.add_argument("--collective", choices=["p2p", "nccl"], default="p2p",
                         help="llama70b_tp: exchange fused into the kernel epilogue (peer stores) or NCCL calls")
     parser.add_argument("--single-layer", type=int, nargs=3, metavar=("K", "N", "M"),

@@ -129,14 +129,80 @@ def load_quantized_model_checkpoint(path: str | os.PathLike) -> dict:
 
 
 def load_packed_model(model: torch.nn.Module, path: str | os.PathLike, device: str | torch.device = "cuda",
-                      fused: bool = True) -> int:
+                      fused: bool = True, *, plan: dict[str, str] | None = None, rank: int | None = None,
+                      world: int | None = None, process_group=None, exchange: str = "nccl", max_rows: int = 8) -> int:
     """Fill ``model`` (typically built on the meta device from a config) from a model checkpoint:
     its linears become packed modules, everything is materialised directly on ``device`` -- FP16
     linear weights never exist -- and the packed tensors are copied in.  Returns the number of
     linears replaced (the reference's ``load_packed_model``, scripts/generate.py:230-257, without the
-    hub download)."""
-    from .integration import load_packed_state_dict
+    hub download).
+
+    With ``plan`` the loader also partitions layers across the ``world`` ranks of a tensor-parallel group
+    while it reads them: ``plan`` maps the last component of a layer's name to ``"column"`` (this rank
+    keeps rows ``[rank*N/world, (rank+1)*N/world)`` of the packed matrix -- a contiguous slab -- and the
+    layer gathers its output) or ``"row"`` (this rank keeps a K slice of every row and the layer sums the
+    partial results), e.g. ``{"q_proj": "column", ..., "down_proj": "row"}`` for a LLaMA block.  Only this
+    rank's shard of a planned layer is ever copied to ``device``.  ``exchange`` picks the modules of
+    ``nibble_b200.sharded`` that do the collectives: ``"nccl"`` (``torch.distributed``; also gloo on CPU
+    ranks) or ``"peer"`` (the kernels' own exchange over peer-mapped memory, batches up to ``max_rows``).
+    ``rank`` / ``world`` default to those of ``process_group``.
+    """
+    from .integration import _restore_computed_buffers, load_packed_state_dict, replace_linear_layers
+    from .linear import QuantizedLinear
 
     checkpoint = load_quantized_model_checkpoint(path)
-    return load_packed_state_dict(model, checkpoint["state_dict"], group_size=checkpoint["group_size"],
-                                  device=device, fused=fused)
+    group_size = checkpoint["group_size"]
+    if not plan:
+        return load_packed_state_dict(model, checkpoint["state_dict"], group_size=group_size, device=device, fused=fused)
+
+    import torch.distributed as dist
+
+    from . import sharded
+
+    if exchange not in ("nccl", "peer"):
+        raise ValueError("exchange must be 'nccl' or 'peer'")
+    if any(cut not in ("column", "row") for cut in plan.values()):
+        raise ValueError("plan values must be 'column' or 'row'")
+    if rank is None:
+        rank = dist.get_rank(process_group)
+    if world is None:
+        world = dist.get_world_size(process_group)
+    state = dict(checkpoint["state_dict"])
+    replaced = replace_linear_layers(model, group_size=group_size, fused=fused, packed_only=True)
+
+    # Take the planned layers out of the tree before it is materialised, so that their full-size packed
+    # storage is never allocated on the device; remember where they sat.
+    planned = []
+    for name, module in list(model.named_modules()):
+        leaf = name.rsplit(".", 1)[-1]
+        if isinstance(module, QuantizedLinear) and leaf in plan:
+            parent = model.get_submodule(name.rsplit(".", 1)[0]) if "." in name else model
+            planned.append((name, leaf, parent, plan[leaf]))
+            setattr(parent, leaf, torch.nn.Identity())
+    shards = {}
+    for name, leaf, parent, cut in planned:
+        packed, scales = state.pop(f"{name}.packed_weights"), state.pop(f"{name}.scales")
+        bias = state.pop(f"{name}.bias", None)
+        _check_pair(packed, scales, group_size)
+        cutter = sharded.shard_rows if cut == "column" else sharded.shard_k
+        extra = () if cut == "column" else (group_size,)
+        shards[name] = tuple(t.to(device) for t in cutter(packed, scales, rank, world, *extra)) + (
+            None if bias is None else bias.to(device),)
+    model.to_empty(device=device)
+    model.load_state_dict(state)
+    _restore_computed_buffers(model)
+    for name, leaf, parent, cut in planned:
+        packed, scales, bias = shards.pop(name)
+        if exchange == "peer":
+            cls = sharded.PeerColumnParallelQuantizedLinear if cut == "column" else sharded.PeerRowParallelQuantizedLinear
+            if bias is not None:
+                raise ValueError(f"layer '{name}' has a bias: the peer exchange modules carry none")
+            layer = cls(packed, scales, group_size, process_group=process_group, max_rows=max_rows)
+            if cut == "row":
+                layer = sharded.SliceInput(layer, rank)
+        elif cut == "column":
+            layer = sharded.ColumnParallelQuantizedLinear(packed, scales, group_size, bias=bias, process_group=process_group)
+        else:
+            layer = sharded.RowParallelQuantizedLinear(packed, scales, group_size, bias=bias, process_group=process_group)
+        setattr(parent, leaf, layer)
+    return replaced

@@ -404,3 +404,15 @@ class PeerRowParallelQuantizedLinear(torch.nn.Module):
         _require_cuda(activations)
         flat = activations.contiguous().reshape(-1, self.in_features)
         return self.finish(self.launch(flat)).reshape(*activations.shape[:-1], self.out_features)
+
+
+class SliceInput(torch.nn.Module):
+    """Feeds a row-parallel layer that wants this rank's K slice from the full activations."""
+
+    def __init__(self, layer: torch.nn.Module, rank: int):
+        super().__init__()
+        self.layer, self.rank = layer, rank
+
+    def forward(self, activations: torch.Tensor) -> torch.Tensor:
+        k = self.layer.in_features
+        return self.layer(activations[..., self.rank * k:(self.rank + 1) * k])

@@ -148,3 +148,34 @@ def test_fused_siblings_one_launch_same_numbers():
         assert got.shape == ref.shape
         torch.testing.assert_close(got, ref, rtol=1e-2, atol=1e-2)
         check_against_oracle(got.reshape(1, -1), x.reshape(1, -1), p, s)
+
+
+def test_model_checkpoint_loads_straight_onto_the_device(tmp_path):
+    """A file in the reference's model-checkpoint format (scripts/generate.py:214-257) into a meta-device model:
+    packed tensors go straight to the GPU, FP16 linear weights never exist, the block computes what the source
+    block computes."""
+    from nibble_b200 import load_packed_model, save_quantized_model_checkpoint
+    from test_fusion_host_logic import Block
+
+    torch.manual_seed(6)
+    source = Block(hidden=1024, kv=256, inter=2048, bias=True).half()
+    assert replace_linear_layers(source, group_size=128) == 7        # quantised on the host
+    path = tmp_path / "model.pt"
+    save_quantized_model_checkpoint(path, source, group_size=128, source_model="gpu-test")
+    with torch.device("meta"):
+        target = Block(hidden=1024, kv=256, inter=2048, bias=True).half()
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    before = torch.cuda.memory_allocated()
+    assert load_packed_model(target, path, device="cuda") == 7
+    delta = torch.cuda.memory_allocated() - before
+    packed_bytes = sum(t.numel() * t.element_size() for t in source.state_dict().values())
+    fp16_bytes = 2 * sum(m.in_features * m.out_features for m in source.modules() if isinstance(m, QuantizedLinear))
+    assert packed_bytes <= delta < fp16_bytes / 2
+    for key, tensor in source.state_dict().items():
+        got = target.state_dict()[key]
+        assert got.is_cuda and torch.equal(got.cpu(), tensor), key
+    x = torch.randn((2, 1024), dtype=torch.float16, device="cuda")
+    q = target.q_proj
+    check_against_oracle(q(x) - q.bias, x, q.packed_weights, q.scales)
+    assert target(x).shape == (2, 1024) and not torch.isnan(target(x)).any()

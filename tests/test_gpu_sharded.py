@@ -98,6 +98,33 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
             torch.testing.assert_close(got.cpu(), torch.from_numpy(c), rtol=3e-2, atol=3e-2)
         for layer in (col_a, col_b, row_c):
             layer.region.check()
+        # a model checkpoint in the reference's dict format, read shard by shard straight onto this rank's GPU
+        from nibble_b200 import load_packed_model, replace_linear_layers, save_quantized_model_checkpoint
+        from nibble_b200.linear import QuantizedLinear
+        from test_fusion_host_logic import Block
+
+        torch.manual_seed(11)
+        source = Block(hidden=512, kv=128, inter=512).half()
+        replace_linear_layers(source, group_size=128)
+        path = os.path.join(out_dir, "model.pt")
+        if rank == 0:
+            save_quantized_model_checkpoint(path, source, group_size=128, source_model="two-gpu-test")
+        dist.barrier()
+        plan = {"q_proj": "column", "k_proj": "column", "v_proj": "column", "o_proj": "column", "gate_proj": "column",
+                "up_proj": "column", "down_proj": "row"}
+        xb = torch.randn((3, 512), generator=torch.Generator().manual_seed(2)).half().cuda()
+        want = source.cuda()(xb)
+        for exchange in ("nccl", "peer"):
+            with torch.device("meta"):
+                target = Block(hidden=512, kv=128, inter=512).half()
+            torch.cuda.synchronize()
+            before = torch.cuda.memory_allocated()
+            assert load_packed_model(target, path, device=f"cuda:{rank}", plan=plan, exchange=exchange) == 7
+            shard = target.k_proj.local.packed_weights
+            assert shard.is_cuda and shard.shape == (128 // world, 256)
+            assert torch.equal(shard, source.k_proj.packed_weights[rank * 64:(rank + 1) * 64])
+            torch.testing.assert_close(target(xb), want, rtol=3e-2, atol=3e-2)
+            torch.testing.assert_close(target(xb), want, rtol=3e-2, atol=3e-2)
         torch.cuda.synchronize()
         dist.barrier()
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
@@ -111,4 +138,4 @@ def test_column_and_row_parallel_over_nccl(tmp_path):
 
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
-    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+    assert sorted(name for name in os.listdir(tmp_path) if name.startswith("ok")) == ["ok0", "ok1"]

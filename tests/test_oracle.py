@@ -181,3 +181,39 @@ def test_torch_port_matches_numpy_oracle(golden):
     assert np.array_equal(port.unpack_codes(packed).numpy(), data["codes"])
     assert np.array_equal(port.dequantize(packed, scales, 128).numpy().view(np.uint32), data["dequant"].view(np.uint32))
     _assert_within_one_half_ulp_step(port.linear(x, packed, scales, 128).numpy(), data["y"])
+
+
+def test_oracle_against_the_compiled_reference_modules(tmp_path):
+    """Where oracle/_ref holds the reference's own CPU modules (oracle/build_ref.py), run them in a child
+    interpreter on seeded data and compare with the numpy oracle: codes, scales and dequantised weights bit for
+    bit, the linear output to within one FP16 step."""
+    import pathlib
+    import subprocess
+    import sys
+
+    root = pathlib.Path(__file__).resolve().parent.parent
+    ref = root / "oracle" / "_ref"
+    if not (ref / "w4a16" / "reference.pyc").is_file():
+        pytest.skip("oracle/_ref is not built (no checkout of the reference on this machine)")
+    out = tmp_path / "ref.npz"
+    script = f"""
+import sys
+sys.path.insert(0, {str(ref)!r})
+import numpy as np, torch
+from w4a16 import quantization as q, reference as r
+assert 'nibble_b200' not in sys.modules
+g = torch.Generator().manual_seed(42)
+w = torch.randn((96, 640), generator=g) * 0.02
+x = torch.randn((5, 640), generator=g).half()
+packed, scales = q.quantize_and_pack_weights(w, 128)
+np.savez({str(out)!r}, w=w.numpy(), x=x.numpy(), packed=packed.numpy(), scales=scales.numpy(),
+         dequant=r.dequantize_weights(packed, scales, 128).numpy(), y=r.linear_reference(x, packed, scales, 128).numpy())
+"""
+    subprocess.run([sys.executable, "-c", script], check=True, cwd=str(tmp_path), timeout=300)
+    data = np.load(out)
+    packed, scales = oracle.quantize_and_pack_weights(data["w"], 128)
+    assert np.array_equal(packed, data["packed"])
+    assert np.array_equal(scales.view(np.uint16), data["scales"].view(np.uint16))
+    deq = oracle.dequantize_weights(packed, scales, 128)
+    assert np.array_equal(deq.view(np.uint32), data["dequant"].view(np.uint32))
+    _assert_within_one_half_ulp_step(oracle.linear_reference(data["x"], packed, scales, 128), data["y"])

@@ -77,15 +77,54 @@ def _worker(rank: int, world: int, port: int, out_dir: str):
         both = [torch.empty_like(got) for _ in range(world)]
         dist.all_gather(both, got)
         assert all(torch.equal(both[0], other) for other in both)
+        _check_sharded_checkpoint_load(rank, world, out_dir)
         open(os.path.join(out_dir, f"ok{rank}"), "w").close()
     finally:
         dist.destroy_process_group()
 
 
+def _check_sharded_checkpoint_load(rank: int, world: int, out_dir: str) -> None:
+    """A model checkpoint in the reference's dict format, read shard by shard: every rank keeps only its rows
+    (column-parallel layers) or its K slice (row-parallel down_proj) and the block still computes what the
+    unsharded block computes."""
+    import nibble_b200.linear as linear_module
+    from nibble_b200 import load_packed_model, replace_linear_layers, save_quantized_model_checkpoint
+    from nibble_b200.sharded import ColumnParallelQuantizedLinear, RowParallelQuantizedLinear
+    from oracle import w4a16_oracle as oracle
+    from test_fusion_host_logic import Block
+
+    def fused(flat, packed, scales, gs):
+        return torch.from_numpy(oracle.linear_reference(flat.numpy(), packed.numpy(), scales.numpy(), gs))
+
+    linear_module._run_fused = fused
+    linear_module._require_cuda = lambda tensor: None
+    torch.manual_seed(11)
+    source = Block(hidden=512, kv=128, inter=512).half()
+    replace_linear_layers(source, group_size=128)
+    path = os.path.join(out_dir, "model.pt")
+    if rank == 0:
+        save_quantized_model_checkpoint(path, source, group_size=128, source_model="gloo-test")
+    dist.barrier()
+    plan = {"q_proj": "column", "k_proj": "column", "v_proj": "column", "o_proj": "column", "gate_proj": "column",
+            "up_proj": "column", "down_proj": "row"}
+    with torch.device("meta"):
+        target = Block(hidden=512, kv=128, inter=512).half()
+    assert load_packed_model(target, path, device="cpu", plan=plan) == 7
+    assert isinstance(target.q_proj, ColumnParallelQuantizedLinear) and isinstance(target.down_proj, RowParallelQuantizedLinear)
+    assert target.k_proj.local.packed_weights.shape == (128 // world, 256)       # this rank's rows only
+    assert target.down_proj.local.packed_weights.shape == (512, 512 // world // 2)  # this rank's K slice only
+    assert torch.equal(target.k_proj.local.packed_weights,
+                       source.k_proj.packed_weights[rank * 64:(rank + 1) * 64])
+    x = torch.randn((3, 512), generator=torch.Generator().manual_seed(2)).half()
+    torch.testing.assert_close(target(x), source(x), rtol=2e-2, atol=2e-2)
+    with pytest.raises(ValueError, match="plan values"):
+        load_packed_model(target, path, device="cpu", plan={"q_proj": "diagonal"})
+
+
 def test_column_and_row_parallel_world_size_2(tmp_path):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
-    assert sorted(os.listdir(tmp_path)) == ["ok0", "ok1"]
+    assert sorted(name for name in os.listdir(tmp_path) if name.startswith("ok")) == ["ok0", "ok1"]
 
 
 def test_shard_helpers():
