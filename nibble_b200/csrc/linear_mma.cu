@@ -839,9 +839,10 @@ linear_mma_kernel(const MmaParams p) {
             if (atomicAdd(p.done_counter, 1u) == ctas - 1) {
                 *p.done_counter = 0u;
                 *p.send_epoch = out_epoch;
+                // one fence orders every CTA's (fenced, counted) stores before all the flag stores that follow
                 __threadfence_system();
                 for (int peer = 0; peer < p.world; ++peer) {
-                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[peer] + p.rank), "r"(out_epoch)
+                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[peer] + p.rank), "r"(out_epoch)
                                  : "memory");
                 }
             }
