@@ -67,9 +67,25 @@ LLAMA70B = {
     "gate_up_proj": (8192, 28672),
     "down_proj": (28672, 8192),
 }
-# Mean DRAM bytes (read + write) per launch of the fused kernel over this workload, from one ncu
-# capture of the timed region (profiles/bench_timed_region_launch_list.md); algorithmic: 3,451,728.
+# Mean DRAM bytes (read + write) per launch of the fused kernel over this workload, from one ncu capture of
+# the timed region (algorithmic: 3,451,728), and the digest of the kernel sources that capture ran: the line
+# reports the figure only while the sources are still those, otherwise null.
 NCU_DRAM_BYTES_PER_LAUNCH = 3513170
+NCU_CAPTURE_SOURCES = ("nibble_b200/csrc/linear_mma.cu", "nibble_b200/csrc/unpack.cuh")
+NCU_CAPTURE_SOURCES_SHA16 = ""
+
+
+def kernel_sources_sha16() -> str:
+    import hashlib
+
+    digest = hashlib.sha256()
+    for name in NCU_CAPTURE_SOURCES:
+        digest.update((ROOT / name).read_bytes())
+    return digest.hexdigest()[:16]
+
+
+def measured_traffic_per_launch():
+    return NCU_DRAM_BYTES_PER_LAUNCH if kernel_sources_sha16() == NCU_CAPTURE_SOURCES_SHA16 else None
 BLOCK_ORDER = ["qo_proj", "kv_proj", "kv_proj", "qo_proj", "gate_up_proj", "gate_up_proj", "down_proj"]
 N_BLOCKS = 22
 
@@ -278,35 +294,49 @@ def prefill_table(torch, device) -> dict:
 
 
 def quantize_table(torch, device) -> dict:
-    """Device quantise+pack and dequantise of one Llama-70B gate/up matrix (28672 x 8192): microseconds and
-    algorithmic GB/s (2.5 bytes per weight with FP16 weights), median of 7 timings of 3 calls."""
-    from nibble_b200 import dequantize_cuda, quantize_and_pack_cuda
+    """Device quantise+pack and dequantise of one Llama-70B gate/up matrix (28672 x 8192) through the C ABI into
+    preallocated outputs: microseconds and algorithmic GB/s (2.5 bytes per weight with FP16 weights), median of 7
+    CUDA-event timings of 20 back-to-back calls each (470 MB per call, so nothing is served from L2)."""
+    import ctypes
 
+    from nibble_b200 import _native
+
+    lib = _native.core()
     k, n = LLAMA70B["gate_up_proj"]
     weights = (torch.randn((n, k), device=device) * 0.02).half()
-    packed, scales = quantize_and_pack_cuda(weights, GROUP)
+    packed = torch.empty((n, k // 2), dtype=torch.uint8, device=device)
+    scales = torch.empty((n, k // GROUP), dtype=torch.float16, device=device)
+    restored = torch.empty_like(weights)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def quantise():
+        assert lib.w4a16_quantize_pack_f16(weights.data_ptr(), packed.data_ptr(), scales.data_ptr(), n, k, GROUP, stream) == 0
+
+    def dequantise():
+        assert lib.w4a16_dequantize_f16(packed.data_ptr(), scales.data_ptr(), restored.data_ptr(), n, k, GROUP, stream) == 0
 
     def timed(fn) -> float:
-        fn()
+        for _ in range(3):
+            fn()
         samples = []
         for _ in range(7):
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             torch.cuda.synchronize()
             start.record()
-            for _ in range(3):
+            for _ in range(20):
                 fn()
             end.record()
             torch.cuda.synchronize()
-            samples.append(start.elapsed_time(end) * 1000.0 / 3)
+            samples.append(start.elapsed_time(end) * 1000.0 / 20)
         return statistics.median(samples)
 
     payload = n * k * 2.5 + n * (k // GROUP) * 2
     peak, _ = measured_peaks()
     out = {}
-    for name, fn in (("quantize_pack_f16", lambda: quantize_and_pack_cuda(weights, GROUP)),
-                     ("dequantize_f16", lambda: dequantize_cuda(packed, scales, GROUP))):
+    for name, fn in (("quantize_pack_f16", quantise), ("dequantize_f16", dequantise)):
         us = timed(fn)
         out[name] = {"us": round(us, 1), "gbs": round(payload / us / 1e3, 1), "frac_measured": round(payload / us / 1e3 / peak, 3)}
+    out["how"] = "C ABI, preallocated outputs, 20 calls per CUDA-event sample, median of 7"
     log(f"  quantise / dequantise 28672 x 8192: {out}")
     return out
 
@@ -1091,7 +1121,7 @@ def run_product(args) -> dict:
         "fused_siblings": fused_siblings,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "peak_kind": peak_kind, "frac_of_8tbs": round(achieved / 8000, 4),
-                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "kernel": "linear_mma_kernel", "mean_launch_us": round(kernel_us, 3),
+                     "traffic": measured_traffic_per_launch(), "kernel": "linear_mma_kernel", "mean_launch_us": round(kernel_us, 3),
                      "bytes_per_launch": step_bytes // len(layers)},
         "clocks": clocks,
     }
@@ -1111,6 +1141,16 @@ def run_product(args) -> dict:
             "llama70b_m1": per_shape_table(torch, LLAMA70B, 1, device, l2, with_cublas=False),
             "llama70b_m8": per_shape_table(torch, LLAMA70B, 8, device, l2, with_cublas=True),
         }
+        short = {"qo_proj": "qo", "kv_proj": "kv", "gate_up_proj": "gate_up", "down_proj": "down", "lm_head": "lm_head"}
+        result["roofline"]["per_layer_frac_m1"] = {
+            **{f"tl_{short[name]}": row["frac_measured"] for name, row in result["layers"]["tinyllama_m1"].items()},
+            **{f"70b_{short[name]}": row["frac_measured"] for name, row in result["layers"]["llama70b_m1"].items()}}
+        result["roofline"]["per_layer_us_m1"] = {
+            **{f"tl_{short[name]}": row["us"] for name, row in result["layers"]["tinyllama_m1"].items()},
+            **{f"70b_{short[name]}": row["us"] for name, row in result["layers"]["llama70b_m1"].items()}}
+        result["roofline"]["m8_vs_cublas_fp16"] = {
+            **{f"tl_{short[name]}": row["speedup_vs_cublas_fp16"] for name, row in result["layers"]["tinyllama_m8"].items()},
+            **{f"70b_{short[name]}": row["speedup_vs_cublas_fp16"] for name, row in result["layers"]["llama70b_m8"].items()}}
         log("prefill-sized batches (tcgen05 kernel)")
         result["prefill"] = prefill_table(torch, device)
         result["quantize"] = quantize_table(torch, device)

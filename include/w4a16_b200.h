@@ -106,39 +106,45 @@ size_t w4a16_linear_workspace_bytes_flags(int64_t M, int64_t N, int64_t K, uint3
 /*
  * Tensor-parallel exchange (no counterpart in the reference, which is single-GPU).  A layer sharded over
  * `world` GPUs of one node hands its result to every GPU from the kernel epilogue -- plain stores into
- * peer-mapped memory over NVLink -- and the kernel that consumes the result waits for it in its own
- * prologue, after its weight prefetch is in flight.  No collective library call, no host involvement.
+ * peer-mapped memory over NVLink -- and the kernel that consumes the result picks it up while it stages its
+ * activations, with its weight prefetch already in flight.  No collective library call, no host involvement,
+ * and no fence or flag round trip on the way: every element travels together with a tag that says which
+ * publication it belongs to, in one naturally atomic store, and the reader simply re-reads an element until
+ * its tag is the one it expects (the low-latency scheme collective libraries use for small messages).
+ *
+ * Element format in a result buffer:
+ *   FP16 results   uint32 = half bits | tag << 16            (element (m, n) at index m * ld + n)
+ *   FP32 partials  uint64 = float bits | (uint64)tag << 32
+ *   tag of publication e = 0x8000 | (e & 0x7FFF); zero-filled memory therefore never looks published.
  *
  * Memory a sharded layer owns on every rank (mapped on all ranks by the caller: CUDA IPC, cuMem, or
  * torch's symmetric memory; zero-filled at start):
  *   two result buffers, `buffer_stride` bytes apart (publication e goes to buffer e & 1),
- *   published[world]  uint32: published[s] = number of the latest complete publication of sender s here,
- *   consumed[world]   uint32: consumed[c]  = latest publication that reader c has finished reading in ITS
+ *   consumed[world]   uint32: consumed[c] = latest publication that reader c has finished reading in ITS
  *                     buffers (readers write it on every rank, so that senders learn when a buffer is free).
  * And private device words on each rank, zero at start: done_counter, send_epoch, staged_counter, status.
  *
- * Sender (w4a16_peer_target): element (m, n) of this rank's result goes to
- * outputs[r] + (e & 1) * buffer_stride, at [m * ld + column_offset + n] (FP16, or FP32 with
- * W4A16_FLAG_OUTPUT_F32), for every rank r, e = *send_epoch + 1.  Before its first store the kernel waits
- * (bounded) until consumed[r] >= e - 2 for all r on this rank; when all its stores are visible system-wide
- * it sets *send_epoch = e and writes e to published[rank] on every rank.  It does not wait for the others.
+ * Sender (w4a16_peer_target): e = *send_epoch + 1.  Before its first store the kernel waits (bounded) until
+ * consumed[r] >= e - 2 for all r on this rank; then every output element (m, n) of this rank's result goes,
+ * tagged, to outputs[r] + (e & 1) * buffer_stride at index m * ld + column_offset + n, for every rank r; the
+ * launch ends by setting *send_epoch = e.  It does not wait for anybody else.
  * Column-parallel layers use it as an all-gather (ld = full N, column_offset = rank * N_local); row-parallel
- * layers push FP32 partials (outputs[r] = staging[r] + rank * M * N floats) and finish with
+ * layers push FP32 partials (outputs[r] = staging[r] + rank * M * N elements) and finish with
  * w4a16_sum_partials_f16.
  *
  * Reader (w4a16_peer_source): after the preceding kernel of the stream has completed it reads
  * e = *epoch (the send_epoch word of the layer that produced the data, on this rank -- so that layer's
- * launch must precede the reader in the stream), waits (bounded) until published[s] >= e for every s, reads
- * from buffer e & 1, and when every CTA has read writes e to consumed[rank] on every rank.
+ * launch must precede the reader in the stream), reads buffer e & 1, re-reading (bounded) every element whose
+ * tag is not yet that of e, and when every CTA has read writes e to consumed[rank] on every rank.
  *
- * Every wait gives up after max_polls polls of one flag and records (which + 1) in *status -- 1..world for
- * a sender that never published, 33..32+world for a reader that never released a buffer -- so a missing
- * rank ends in an error the host can read, never in a hung GPU.  Every rank must issue the same sequence
- * of launches for a layer, and every publication must be read (by one reader) on every rank.
+ * Every wait gives up after max_polls polls and records who was missing in *status -- 1 + sender for an
+ * element that never arrived (the sender is worked out from the element's column: first_column and
+ * columns_per_rank; for FP32 partials it is the slot), 33 + reader for a reader that never released a buffer --
+ * so a missing rank ends in an error the host can read, never in a hung GPU.  Every rank must issue the same
+ * sequence of launches for a layer, and every publication must be read (by one reader) on every rank.
  */
 typedef struct w4a16_peer_target {
     void* const* outputs;         /* [world] result buffer 0 of this layer on each rank (plus this rank's offset)   */
-    uint32_t* const* published;   /* [world] the published[] array of each rank                                      */
     const uint32_t* consumed;     /* this rank's consumed[] array                                                     */
     uint32_t* done_counter;
     uint32_t* send_epoch;
@@ -153,20 +159,22 @@ typedef struct w4a16_peer_target {
 
 typedef struct w4a16_peer_source {
     const uint32_t* epoch;        /* send_epoch word of the producing layer on this rank                              */
-    const uint32_t* published;    /* this rank's published[] array of the producing layer                             */
     uint32_t* const* consumed;    /* [world] the consumed[] array of each rank                                        */
     uint32_t* staged_counter;
     uint32_t* status;
     int64_t buffer_stride;
     int64_t max_polls;
+    int64_t first_column;         /* column of the gathered result that x (or the copy) starts at                     */
+    int64_t columns_per_rank;     /* columns each sender contributes (0: unknown, failures are reported as sender 0)  */
     int32_t rank;
     int32_t world;
 } w4a16_peer_source;
 
 /* w4a16_linear_f16 as one stage of a tensor-parallel chain (fast path only: group 128, aligned pointers,
  * M <= 64; otherwise W4A16_ERR_BAD_CONFIG).  `target` non-NULL: the result goes to every rank as described
- * above and y is ignored; NULL: the result goes to y.  `source` non-NULL: x points into result buffer 0 of
- * the producing layer on this rank and the kernel adds the parity offset after its wait; NULL: plain x.
+ * above and y is ignored; NULL: the result goes to y.  `source` non-NULL: x points at tagged FP16 elements
+ * (4 bytes each) in result buffer 0 of the producing layer on this rank and the kernel adds the parity
+ * offset itself; NULL: plain FP16 x.
  * x_ld is the distance between batch rows of x in elements (>= K, a multiple of 8), so that a column slice of
  * a wider gathered result can be the input. */
 int w4a16_linear_f16_peers(const void* x, int64_t x_ld, const void* packed, const void* scales, void* y,
@@ -175,15 +183,17 @@ int w4a16_linear_f16_peers(const void* x, int64_t x_ld, const void* packed, cons
                            const w4a16_peer_target* target, const w4a16_peer_source* source,
                            w4a16_stream_t stream);
 
-/* Reader as a kernel of its own: waits for the publication described by `source`, copies `bytes` bytes
- * (a multiple of 16) from the current result buffer (`buffer0` + parity offset) to `out` when out is
- * non-NULL, then releases the buffer. */
-int w4a16_wait_peers(const w4a16_peer_source* source, const void* buffer0, void* out, int64_t bytes,
+/* Reader as a kernel of its own: copies `count` FP16 elements (a multiple of 8) of the publication described
+ * by `source` from the current result buffer (`buffer0` + parity offset, tagged elements) to `out` (plain
+ * FP16), waiting for elements that have not arrived yet, then releases the buffer.  count may be 0 (release
+ * only: for a result nobody needs). */
+int w4a16_wait_peers(const w4a16_peer_source* source, const void* buffer0, void* out, int64_t count,
                      uint32_t flags, w4a16_stream_t stream);
 
 /* y[i] = half(sum_r partials[r * count + i]), r ascending: the finish of a row-parallel layer.
- * With `source` non-NULL `partials` is result buffer 0 of the layer and the kernel is the reader of the
- * publication (wait, parity offset, release) as above; NULL: a plain sum over a local array.
+ * With `source` non-NULL `partials` is result buffer 0 of the layer (tagged FP32 elements, 8 bytes each) and
+ * the kernel is the reader of the publication (parity offset, wait per element, release) as above; NULL: a
+ * plain sum over a local float array.
  * flags (here and for w4a16_wait_peers): W4A16_FLAG_PROGRAMMATIC_LAUNCH only. */
 int w4a16_sum_partials_f16(const void* partials, void* y, int64_t count, int32_t world,
                            const w4a16_peer_source* source, uint32_t flags, w4a16_stream_t stream);

@@ -33,7 +33,6 @@ class PeerTarget(ctypes.Structure):
 
     _fields_ = [
         ("outputs", ctypes.c_void_p),
-        ("published", ctypes.c_void_p),
         ("consumed", ctypes.c_void_p),
         ("done_counter", ctypes.c_void_p),
         ("send_epoch", ctypes.c_void_p),
@@ -52,12 +51,13 @@ class PeerSource(ctypes.Structure):
 
     _fields_ = [
         ("epoch", ctypes.c_void_p),
-        ("published", ctypes.c_void_p),
         ("consumed", ctypes.c_void_p),
         ("staged_counter", ctypes.c_void_p),
         ("status", ctypes.c_void_p),
         ("buffer_stride", ctypes.c_int64),
         ("max_polls", ctypes.c_int64),
+        ("first_column", ctypes.c_int64),
+        ("columns_per_rank", ctypes.c_int64),
         ("rank", ctypes.c_int32),
         ("world", ctypes.c_int32),
     ]

@@ -184,9 +184,12 @@ int w4a16_linear_f16_peers(const void* x, int64_t x_ld, const void* packed, cons
                                     (flags & W4A16_FLAG_OUTPUT_F32) != 0, reinterpret_cast<cudaStream_t>(stream));
 }
 
-int w4a16_wait_peers(const w4a16_peer_source* source, const void* buffer0, void* out, int64_t bytes, uint32_t flags,
+int w4a16_wait_peers(const w4a16_peer_source* source, const void* buffer0, void* out, int64_t count, uint32_t flags,
                      w4a16_stream_t stream) {
-    return w4a16::launch_wait_peers(source, buffer0, out, bytes, (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0,
+    const int64_t ld = source != nullptr && source->columns_per_rank > 0
+                           ? source->columns_per_rank * static_cast<int64_t>(source->world)
+                           : 0;
+    return w4a16::launch_wait_peers(source, buffer0, out, count, ld, (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0,
                                     reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -196,7 +199,7 @@ int w4a16_sum_partials_f16(const void* partials, void* y, int64_t count, int32_t
     if (count == 0) return W4A16_OK;
     if (partials == nullptr || y == nullptr) return W4A16_ERR_NULL_POINTER;
     if (source != nullptr && source->world != world) return W4A16_ERR_BAD_SHAPE;
-    return w4a16::launch_sum_partials(static_cast<const float*>(partials), static_cast<__half*>(y), count, world, source,
+    return w4a16::launch_sum_partials(partials, static_cast<__half*>(y), count, world, source,
                                       (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0, reinterpret_cast<cudaStream_t>(stream));
 }
 

@@ -56,9 +56,9 @@ int launch_linear_generic(const LinearProblem& p, bool out_f32, cudaStream_t str
 
 // Tensor-parallel helpers: a reader kernel (bounded wait for every rank's publication, optional copy, release)
 // and the rank-ordered sum of FP32 partials into FP16.
-int launch_wait_peers(const w4a16_peer_source* source, const void* buffer0, void* out, int64_t bytes, bool programmatic,
-                      cudaStream_t stream);
-int launch_sum_partials(const float* partials, __half* y, int64_t count, int world, const w4a16_peer_source* source,
+int launch_wait_peers(const w4a16_peer_source* source, const void* buffer0, void* out, int64_t count, int64_t ld,
+                      bool programmatic, cudaStream_t stream);
+int launch_sum_partials(const void* partials, __half* y, int64_t count, int world, const w4a16_peer_source* source,
                         bool programmatic, cudaStream_t stream);
 
 int launch_dequantize(const uint8_t* packed, const __half* scales, __half* weights, int64_t N,

@@ -69,7 +69,6 @@ struct MmaParams {
     int out_f32;
     // Optional fan-out of the result to every GPU of a tensor-parallel group (null: plain y).
     void* const* peer_out;          // [world] result buffer 0 of this layer on each rank
-    unsigned* const* peer_flags;    // [world] each rank's published[] flags, indexed by sender
     const unsigned* consumed;       // this rank's consumed[] flags, indexed by reader
     unsigned* done_counter;         // CTAs of this launch that finished; left at zero
     unsigned* send_epoch;           // publications made so far by this layer on this rank
@@ -81,10 +80,11 @@ struct MmaParams {
     int rank, world;
     // Optional: x is the published result of another sharded layer (null: plain x).
     const unsigned* src_epoch;      // that layer's send_epoch word on this rank
-    const unsigned* src_published;  // this rank's published[] flags of that layer
     unsigned* const* src_consumed;  // [world] consumed[] flags of that layer on each rank
     unsigned* staged_counter;       // CTAs of this launch that have read x; left at zero
     long long src_stride;           // bytes between that layer's two result buffers
+    long long src_col0;             // column of the gathered result x starts at, and columns per sender:
+    long long src_cols_per_rank;    //   they name the sender of an element that never arrives
     // Activations derived while they are staged (W4A16_INPUT_*): see the staging code.
     int x_mode;
     long long x_ld;                 // elements between batch rows of x (2K for [gate | up] rows)
@@ -123,6 +123,15 @@ __device__ __forceinline__ uint4 silu_mul8(const uint4& gate, const uint4& up) {
     return as_uint4(out);
 }
 
+// True once some wait of this layer has already given up: later waits then do not spend their own limit, so a
+// missing rank costs one time-out, not one per element.
+__device__ __forceinline__ bool already_failed(const unsigned* status) {
+    if (status == nullptr) return false;
+    unsigned seen;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(seen) : "l"(status));
+    return seen != 0u;
+}
+
 // Bounded wait, by the first `world` lanes of one warp, until flags[lane] has reached `epoch`.  A flag that
 // never gets there is recorded in *status as code_base + lane + 1 and the wait moves on: the caller then
 // computes on unfinished data and the host reads the status word, but the GPU never hangs.
@@ -138,6 +147,7 @@ __device__ __forceinline__ void wait_for_flags(const unsigned* flags, int world,
                 arrived = true;
                 break;
             }
+            if ((poll & 255) == 255 && already_failed(status)) break;
             __nanosleep(20);
         }
         if (!arrived && status != nullptr) atomicMax(status, code_base + static_cast<unsigned>(lane) + 1u);
@@ -152,6 +162,60 @@ __device__ __forceinline__ void release_buffers(unsigned* const* consumed, int r
     for (int peer = 0; peer < world; ++peer) {
         asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(consumed[peer] + rank), "r"(epoch) : "memory");
     }
+}
+
+// Results travel between GPUs as tagged elements: a 32-bit word holding an FP16 value and the 16-bit tag of
+// the publication it belongs to, or a 64-bit word holding an FP32 value and the tag.  One aligned store of
+// such a word is atomic, so a reader that sees the expected tag also sees the value: no fence, no flag.
+__device__ __forceinline__ unsigned tag_of(unsigned epoch) { return 0x8000u | (epoch & 0x7FFFu); }
+
+__device__ __forceinline__ void store_tagged_half(void* buffer, size_t index, float value, unsigned tag) {
+    const unsigned word = static_cast<unsigned>(__half_as_ushort(__float2half_rn(value))) | (tag << 16);
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(static_cast<unsigned*>(buffer) + index), "r"(word) : "memory");
+}
+__device__ __forceinline__ void store_tagged_float(void* buffer, size_t index, float value, unsigned tag) {
+    const unsigned long long word = static_cast<unsigned long long>(__float_as_uint(value)) |
+                                    (static_cast<unsigned long long>(tag) << 32);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(static_cast<unsigned long long*>(buffer) + index), "l"(word)
+                 : "memory");
+}
+
+// Eight tagged FP16 elements (32 bytes, 32-byte aligned), read past L1.
+struct Tagged8 {
+    uint4 a, b;
+};
+__device__ __forceinline__ Tagged8 load_tagged8(const uint4* src) {
+    Tagged8 t;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.a.x), "=r"(t.a.y), "=r"(t.a.z), "=r"(t.a.w) : "l"(src));
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(t.b.x), "=r"(t.b.y), "=r"(t.b.z), "=r"(t.b.w) : "l"(src + 1));
+    return t;
+}
+// True when all eight carry `tag2` (the tag in both halves of a word).
+__device__ __forceinline__ bool tags_match(const Tagged8& t, unsigned tag2) {
+    return prmt(t.a.x, t.a.y, 0x7632u) == tag2 && prmt(t.a.z, t.a.w, 0x7632u) == tag2 &&
+           prmt(t.b.x, t.b.y, 0x7632u) == tag2 && prmt(t.b.z, t.b.w, 0x7632u) == tag2;
+}
+// The eight FP16 values, in order.
+__device__ __forceinline__ uint4 values_of(const Tagged8& t) {
+    return make_uint4(prmt(t.a.x, t.a.y, 0x5410u), prmt(t.a.z, t.a.w, 0x5410u), prmt(t.b.x, t.b.y, 0x5410u),
+                      prmt(t.b.z, t.b.w, 0x5410u));
+}
+// Re-reads (bounded) until the eight elements at `src` carry the tag; false when the wait ran out.
+__device__ __forceinline__ bool wait_tagged8(const uint4* src, unsigned tag2, long long max_polls, const unsigned* status,
+                                             Tagged8& t) {
+    for (long long poll = 0; poll < max_polls; ++poll) {
+        if (tags_match(t, tag2)) return true;
+        if ((poll & 255) == 255 && already_failed(status)) break;
+        __nanosleep(20);
+        t = load_tagged8(src);
+    }
+    return tags_match(t, tag2);
+}
+// Which sender owns `column` of a gathered result (for the status word).
+__device__ __forceinline__ unsigned sender_of(long long column, long long columns_per_rank, int world) {
+    if (columns_per_rank <= 0) return 0u;
+    const long long sender = column / columns_per_rank;
+    return static_cast<unsigned>(sender < world ? sender : world - 1);
 }
 
 __device__ __forceinline__ void group_barrier(int id, int threads) {
@@ -210,6 +274,48 @@ __host__ __device__ constexpr int stage_bytes() {
 template <int NT, int TILES>
 __host__ __device__ constexpr int min_ctas_per_sm() {
     return (NT * TILES <= 2) ? 2 : 1;
+}
+
+// Stages x from another sharded layer's result buffer: tagged elements arriving from every rank.  Four pieces
+// are requested per round, then the ones whose tag is not yet this publication's are re-read (bounded).
+// Kept out of line so that its registers do not count against the streaming loop of the kernel.
+// Destination layout: see the staging comment in the kernel (16-byte unit ((c*4 + i) * XB + n) * 4 + t).
+template <int XB>
+__device__ __noinline__ void stage_tagged(const uint4* base, size_t row_units, int units_per_row, int rows, unsigned tag,
+                                          unsigned xs, long long max_polls, unsigned* status, long long first_column,
+                                          long long cols_per_rank, int world) {
+    const unsigned tag2 = tag | (tag << 16);
+    const int total = units_per_row * rows;
+    for (int i0 = threadIdx.x; i0 < total; i0 += 4 * kThreads) {
+        Tagged8 t[4];
+        const uint4* src[4];
+        int at[4], row[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int i = i0 + r * kThreads;
+            if (i < total) {
+                row[r] = XB == 1 ? 0 : i / units_per_row;
+                at[r] = XB == 1 ? i : i - row[r] * units_per_row;
+                src[r] = base + row[r] * row_units + 2 * at[r];
+                t[r] = load_tagged8(src[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            if (i0 + r * kThreads < total) {
+                if (!wait_tagged8(src[r], tag2, max_polls, status, t[r]) && status != nullptr) {
+                    atomicMax(status, sender_of(first_column + at[r] * 8, cols_per_rank, world) + 1u);
+                }
+                const uint4 q = values_of(t[r]);
+                const int j = at[r];
+                const int c = j >> 4, tt = (j >> 2) & 3, i = j & 3;
+                const unsigned dst = xs + (((c * 4 + i) * XB + row[r]) * 4 + tt) * 16;
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(prmt(q.x, q.z, 0x5410u)),
+                             "r"(prmt(q.x, q.z, 0x7632u)), "r"(prmt(q.y, q.w, 0x5410u)), "r"(prmt(q.y, q.w, 0x7632u))
+                             : "memory");
+            }
+        }
+    }
 }
 
 // NT     n8 tiles of the batch a CTA handles per pass (batch rows = up to 8*NT)
@@ -359,23 +465,22 @@ linear_mma_kernel(const MmaParams p) {
     pdl_release_downstream();
     pdl_wait_for_upstream();
 
-    // Tensor-parallel hand-shakes, with the weight ring already in flight: as a reader, wait until every
-    // rank's part of x has landed here; as a sender, until every rank has let go of the result buffer this
-    // launch will overwrite (two publications back, so this is normally satisfied long ago).
+    // Tensor-parallel hand-shakes, with the weight ring already in flight.  As a sender: wait until every rank
+    // has let go of the result buffer this launch will overwrite (two publications back, so this is normally
+    // satisfied long ago).  As a reader nothing is waited for here: the staging loop below re-reads elements
+    // of x that have not arrived yet.
     const __half* x_in = p.x;
-    unsigned src_epoch = 0, out_epoch = 0;
+    unsigned src_epoch = 0, out_epoch = 0, out_tag = 0;
     size_t out_offset = 0;
-    if (p.src_epoch != nullptr || p.peer_out != nullptr) {
-        if (p.src_epoch != nullptr) {
-            src_epoch = __ldcg(p.src_epoch);
-            if (warp == 0) wait_for_flags(p.src_published, p.world, src_epoch, p.wait_polls, p.peer_status, 0u);
-            x_in = reinterpret_cast<const __half*>(reinterpret_cast<const char*>(p.x) + (src_epoch & 1u) * p.src_stride);
-        }
-        if (p.peer_out != nullptr) {
-            out_epoch = __ldcg(p.send_epoch) + 1u;
-            if (warp == 1) wait_for_flags(p.consumed, p.world, out_epoch - 2u, p.wait_polls, p.peer_status, kReaderCodeBase);
-            out_offset = static_cast<size_t>(out_epoch & 1u) * static_cast<size_t>(p.out_stride);
-        }
+    if (p.src_epoch != nullptr) {
+        src_epoch = __ldcg(p.src_epoch);
+        x_in = reinterpret_cast<const __half*>(reinterpret_cast<const char*>(p.x) + (src_epoch & 1u) * p.src_stride);
+    }
+    if (p.peer_out != nullptr) {
+        out_epoch = __ldcg(p.send_epoch) + 1u;
+        out_tag = tag_of(out_epoch);
+        if (warp == 1) wait_for_flags(p.consumed, p.world, out_epoch - 2u, p.wait_polls, p.peer_status, kReaderCodeBase);
+        out_offset = static_cast<size_t>(out_epoch & 1u) * static_cast<size_t>(p.out_stride);
         __syncthreads();
     }
 
@@ -395,7 +500,15 @@ linear_mma_kernel(const MmaParams p) {
                          "r"(prmt(q.y, q.w, 0x7632u))
                          : "memory");
         };
-        if (p.x_mode == W4A16_INPUT_ADD_RMSNORM) {
+        if (p.src_epoch != nullptr) {
+            const int staged_rows = XB == 1 ? 1 : batch_here;
+            const uint4* base = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned*>(x_in) +
+                                                               static_cast<size_t>(m0) * p.x_ld +
+                                                               static_cast<size_t>(c_begin) * kGroup);
+            stage_tagged<XB>(base, static_cast<size_t>(p.x_ld) >> 2, units_per_row, staged_rows, tag_of(src_epoch), xs,
+                             p.wait_polls, p.peer_status, p.src_col0 + static_cast<long long>(c_begin) * kGroup,
+                             p.src_cols_per_rank, p.world);
+        } else if (p.x_mode == W4A16_INPUT_ADD_RMSNORM) {
             // pass 1, whole row: s = half(stream + delta), sum of squares in FP32
             const uint4* s_in = reinterpret_cast<const uint4*>(x_in);
             const uint4* d_in = reinterpret_cast<const uint4*>(p.x_second);
@@ -655,9 +768,9 @@ linear_mma_kernel(const MmaParams p) {
             for (int peer = 0; peer < p.world; ++peer) {
                 char* buffer = static_cast<char*>(p.peer_out[peer]) + out_offset;
                 if (p.out_f32) {
-                    reinterpret_cast<float*>(buffer)[at] = sum;
+                    store_tagged_float(buffer, at, sum, out_tag);
                 } else {
-                    reinterpret_cast<__half*>(buffer)[at] = __float2half_rn(sum);
+                    store_tagged_half(buffer, at, sum, out_tag);
                 }
             }
         }
@@ -829,23 +942,13 @@ linear_mma_kernel(const MmaParams p) {
     }
     cp_async_wait<0>();   // nothing of this thread may still be landing in shared memory at exit
 
-    if (p.peer_out != nullptr) {
-        // Publish: once every CTA of the launch has made its peer stores visible system-wide, the
-        // last one to finish records the publication and writes its number to published[rank] on every rank.
-        __syncthreads();
-        if (tid == 0) {
-            __threadfence_system();
-            const unsigned ctas = gridDim.x * gridDim.y * gridDim.z;
-            if (atomicAdd(p.done_counter, 1u) == ctas - 1) {
-                *p.done_counter = 0u;
-                *p.send_epoch = out_epoch;
-                // one fence orders every CTA's (fenced, counted) stores before all the flag stores that follow
-                __threadfence_system();
-                for (int peer = 0; peer < p.world; ++peer) {
-                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[peer] + p.rank), "r"(out_epoch)
-                                 : "memory");
-                }
-            }
+    if (p.peer_out != nullptr && tid == 0) {
+        // The tagged elements need no flag behind them; the last CTA only counts the publication, for this
+        // rank's readers (which run after this kernel has completed) and for the next launch.
+        const unsigned ctas = gridDim.x * gridDim.y * gridDim.z;
+        if (atomicAdd(p.done_counter, 1u) == ctas - 1) {
+            *p.done_counter = 0u;
+            *p.send_epoch = out_epoch;
         }
     }
 }
@@ -853,22 +956,14 @@ linear_mma_kernel(const MmaParams p) {
 // What a kernel needs to be the reader of a sharded layer's publication.
 struct ReaderParams {
     const unsigned* epoch;
-    const unsigned* published;
     unsigned* const* consumed;
     unsigned* staged_counter;
     unsigned* status;
     long long stride;
     long long max_polls;
+    long long col0, cols_per_rank;
     int rank, world;
 };
-
-// Block-wide: waits (bounded) for the publication, returns its number; every thread gets it.
-__device__ __forceinline__ unsigned reader_wait(const ReaderParams& r) {
-    const unsigned epoch = __ldcg(r.epoch);
-    if (threadIdx.x < 32) wait_for_flags(r.published, r.world, epoch, r.max_polls, r.status, 0u);
-    __syncthreads();
-    return epoch;
-}
 
 // Block-wide: the last block of the grid to get here gives the buffers back to the senders.
 __device__ __forceinline__ void reader_release(const ReaderParams& r, unsigned epoch) {
@@ -882,41 +977,76 @@ __device__ __forceinline__ void reader_release(const ReaderParams& r, unsigned e
     }
 }
 
-// A reader as a kernel of its own: waits for the publication, optionally copies it out of the result buffer
-// (16-byte units), releases the buffer.
-__global__ void wait_peers_kernel(const ReaderParams r, const uint4* buffer0, uint4* out, long long units) {
+// A reader as a kernel of its own: copies `units` groups of eight FP16 values of the publication out of the
+// result buffer (tagged elements -> plain FP16), re-reading what has not arrived yet, then releases the buffer.
+// `ld` is the row length of the gathered result in elements (names the sender of a missing element).
+__global__ void wait_peers_kernel(const ReaderParams r, const uint4* buffer0, uint4* out, long long units, long long ld) {
     pdl_release_downstream();
     pdl_wait_for_upstream();
-    const unsigned epoch = reader_wait(r);
-    if (out != nullptr) {
-        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(buffer0) + (epoch & 1u) * r.stride);
-        for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < units;
-             i += static_cast<long long>(gridDim.x) * blockDim.x) {
-            out[i] = __ldcg(src + i);
+    const unsigned epoch = __ldcg(r.epoch);
+    const unsigned tag = tag_of(epoch);
+    const unsigned tag2 = tag | (tag << 16);
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(buffer0) + (epoch & 1u) * r.stride);
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < units;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        Tagged8 t = load_tagged8(src + 2 * i);
+        if (!wait_tagged8(src + 2 * i, tag2, r.max_polls, r.status, t)) {
+            const long long column = r.col0 + (ld > 0 ? (i * 8) % ld : 0);
+            atomicMax(r.status, sender_of(column, r.cols_per_rank, r.world) + 1u);
         }
+        out[i] = values_of(t);
     }
     reader_release(r, epoch);
 }
 
 // y = half(sum over ranks of partials[rank]), summed in rank order so every rank gets identical bits.
-// With a reader description the block first waits (bounded) for every rank's publication, reads the
-// partials of that publication's buffer and releases it afterwards.
-__global__ void sum_partials_kernel(const float* __restrict__ partials, __half* __restrict__ y, long long count,
+// With a reader description the partials are tagged 64-bit elements of a publication: each is re-read
+// (bounded) until it has arrived, and the buffer is released afterwards.
+__global__ void sum_partials_kernel(const void* __restrict__ partials, __half* __restrict__ y, long long count,
                                     int world, const ReaderParams r) {
     pdl_release_downstream();
     pdl_wait_for_upstream();
-    unsigned epoch = 0;
-    if (r.epoch != nullptr) {
-        epoch = reader_wait(r);
-        partials = reinterpret_cast<const float*>(reinterpret_cast<const char*>(partials) + (epoch & 1u) * r.stride);
-    }
     const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (r.epoch == nullptr) {
+        if (i < count) {
+            float sum = 0.f;
+            for (int k = 0; k < world; ++k) sum += __ldcg(static_cast<const float*>(partials) + static_cast<long long>(k) * count + i);
+            y[i] = __float2half_rn(sum);
+        }
+        return;
+    }
+    const unsigned epoch = __ldcg(r.epoch);
+    const unsigned long long tag = tag_of(epoch);
+    const unsigned long long* src = reinterpret_cast<const unsigned long long*>(
+        static_cast<const char*>(partials) + (epoch & 1u) * r.stride);
     if (i < count) {
         float sum = 0.f;
-        for (int k = 0; k < world; ++k) sum += __ldcg(partials + static_cast<long long>(k) * count + i);
+        for (int k0 = 0; k0 < world; k0 += 8) {
+            unsigned long long v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (k0 + j < world) {
+                    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v[j]) : "l"(src + static_cast<long long>(k0 + j) * count + i));
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (k0 + j < world) {
+                    const unsigned long long* at = src + static_cast<long long>(k0 + j) * count + i;
+                    long long poll = 0;
+                    while ((v[j] >> 32) != tag && poll++ < r.max_polls) {
+                        if ((poll & 255) == 255 && already_failed(r.status)) break;
+                        __nanosleep(20);
+                        asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v[j]) : "l"(at));
+                    }
+                    if ((v[j] >> 32) != tag) atomicMax(r.status, static_cast<unsigned>(k0 + j) + 1u);
+                    sum += __uint_as_float(static_cast<unsigned>(v[j]));
+                }
+            }
+        }
         y[i] = __float2half_rn(sum);
     }
-    if (r.epoch != nullptr) reader_release(r, epoch);
+    reader_release(r, epoch);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1094,16 +1224,16 @@ namespace {
 int reader_params(const w4a16_peer_source* source, ReaderParams* r) {
     *r = ReaderParams{};
     if (source == nullptr) return W4A16_OK;
-    if (source->epoch == nullptr || source->published == nullptr || source->consumed == nullptr ||
-        source->staged_counter == nullptr || source->status == nullptr) {
+    if (source->epoch == nullptr || source->consumed == nullptr || source->staged_counter == nullptr ||
+        source->status == nullptr) {
         return W4A16_ERR_NULL_POINTER;
     }
     if (source->world < 1 || source->world > 32 || source->rank < 0 || source->rank >= source->world ||
-        source->max_polls <= 0 || source->buffer_stride < 0) {
+        source->max_polls <= 0 || source->buffer_stride < 0 || source->first_column < 0 || source->columns_per_rank < 0) {
         return W4A16_ERR_BAD_SHAPE;
     }
-    *r = ReaderParams{source->epoch, source->published, source->consumed, source->staged_counter, source->status,
-                      source->buffer_stride, source->max_polls, source->rank, source->world};
+    *r = ReaderParams{source->epoch, source->consumed, source->staged_counter, source->status, source->buffer_stride,
+                      source->max_polls, source->first_column, source->columns_per_rank, source->rank, source->world};
     return W4A16_OK;
 }
 
@@ -1125,29 +1255,35 @@ int launch_small(Kernel kernel, unsigned blocks, unsigned threads, bool programm
 
 }  // namespace
 
-int launch_wait_peers(const w4a16_peer_source* source, const void* buffer0, void* out, int64_t bytes, bool programmatic,
-                      cudaStream_t stream) {
+int launch_wait_peers(const w4a16_peer_source* source, const void* buffer0, void* out, int64_t count, int64_t ld,
+                      bool programmatic, cudaStream_t stream) {
     if (source == nullptr) return W4A16_ERR_NULL_POINTER;
     ReaderParams r;
     const int status = reader_params(source, &r);
     if (status != W4A16_OK) return status;
-    if (bytes < 0 || bytes % 16 != 0) return W4A16_ERR_BAD_SHAPE;
-    if (out != nullptr && (buffer0 == nullptr || reinterpret_cast<uintptr_t>(buffer0) % 16 != 0 ||
-                           reinterpret_cast<uintptr_t>(out) % 16 != 0 || source->buffer_stride % 16 != 0)) {
-        return W4A16_ERR_MISALIGNED;
+    if (count < 0 || count % 8 != 0) return W4A16_ERR_BAD_SHAPE;
+    if (count > 0) {
+        if (buffer0 == nullptr || out == nullptr) return W4A16_ERR_NULL_POINTER;
+        if (reinterpret_cast<uintptr_t>(buffer0) % 32 != 0 || reinterpret_cast<uintptr_t>(out) % 16 != 0 ||
+            source->buffer_stride % 32 != 0) {
+            return W4A16_ERR_MISALIGNED;
+        }
     }
-    const long long units = out != nullptr ? bytes / 16 : 0;
-    const unsigned blocks = static_cast<unsigned>(std::min<long long>(32, std::max<long long>(1, (units + 255) / 256)));
+    const long long units = count / 8;
+    const unsigned blocks = static_cast<unsigned>(std::min<long long>(64, std::max<long long>(1, (units + 255) / 256)));
     return launch_small(wait_peers_kernel, blocks, 256, programmatic, stream, r, static_cast<const uint4*>(buffer0),
-                        static_cast<uint4*>(out), units);
+                        static_cast<uint4*>(out), units, static_cast<long long>(ld));
 }
 
-int launch_sum_partials(const float* partials, __half* y, int64_t count, int world, const w4a16_peer_source* source,
+int launch_sum_partials(const void* partials, __half* y, int64_t count, int world, const w4a16_peer_source* source,
                         bool programmatic, cudaStream_t stream) {
     if (count <= 0) return W4A16_OK;
     ReaderParams r;
     const int status = reader_params(source, &r);
     if (status != W4A16_OK) return status;
+    if (source != nullptr && (reinterpret_cast<uintptr_t>(partials) % 8 != 0 || source->buffer_stride % 8 != 0)) {
+        return W4A16_ERR_MISALIGNED;
+    }
     const int threads = 256;
     const int64_t blocks = (count + threads - 1) / threads;
     if (blocks > INT32_MAX) return W4A16_ERR_TOO_LARGE;
@@ -1206,7 +1342,6 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
     params.row_tiles_total = static_cast<int>((prob.N + 16 * cfg.row_tiles - 1) / (16 * cfg.row_tiles));
     params.out_f32 = out_f32 ? 1 : 0;
     params.peer_out = nullptr;
-    params.peer_flags = nullptr;
     params.done_counter = nullptr;
     params.send_epoch = nullptr;
     params.peer_status = nullptr;
@@ -1243,8 +1378,9 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
     params.consumed = nullptr;
     params.out_stride = 0;
     params.src_epoch = nullptr;
-    params.src_published = nullptr;
     params.src_consumed = nullptr;
+    params.src_col0 = 0;
+    params.src_cols_per_rank = 0;
     params.staged_counter = nullptr;
     params.src_stride = 0;
     if (prob.x_ld != 0) {
@@ -1253,7 +1389,7 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
     }
     if (prob.peers != nullptr) {
         const w4a16_peer_target& t = *prob.peers;
-        if (t.outputs == nullptr || t.published == nullptr || t.consumed == nullptr || t.done_counter == nullptr ||
+        if (t.outputs == nullptr || t.consumed == nullptr || t.done_counter == nullptr ||
             t.send_epoch == nullptr || t.status == nullptr) {
             return W4A16_ERR_NULL_POINTER;
         }
@@ -1262,7 +1398,6 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
             return W4A16_ERR_BAD_SHAPE;
         }
         params.peer_out = t.outputs;
-        params.peer_flags = t.published;
         params.consumed = t.consumed;
         params.done_counter = t.done_counter;
         params.send_epoch = t.send_epoch;
@@ -1278,10 +1413,14 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
         ReaderParams r;
         const int status = reader_params(prob.source, &r);
         if (status != W4A16_OK) return status;
-        if (params.x_mode != W4A16_INPUT_PLAIN || r.stride % 16 != 0) return W4A16_ERR_BAD_CONFIG;
+        // tagged elements are 4 bytes each and are read 32 bytes at a time
+        if (params.x_mode != W4A16_INPUT_PLAIN || r.stride % 32 != 0 || reinterpret_cast<uintptr_t>(prob.x) % 32 != 0) {
+            return W4A16_ERR_BAD_CONFIG;
+        }
         if (prob.peers != nullptr && (prob.peers->world != r.world || prob.peers->rank != r.rank)) return W4A16_ERR_BAD_SHAPE;
         params.src_epoch = r.epoch;
-        params.src_published = r.published;
+        params.src_col0 = r.col0;
+        params.src_cols_per_rank = r.cols_per_rank;
         params.src_consumed = r.consumed;
         params.staged_counter = r.staged_counter;
         params.src_stride = r.stride;

@@ -47,6 +47,10 @@ class FusedQuantizedLinear(QuantizedLinear):
         scales = torch.cat([part.scales for part in parts], dim=0).contiguous()
         bias = None if first.bias is None else torch.cat([part.bias for part in parts], dim=0).contiguous()
         super().__init__(packed, scales, first.group_size, bias=bias, fused=first.fused)
+        # The fused tensors stay out of state dicts: every FusedSlice saves and loads its own rows under the
+        # name its layer always had, so checkpoints do not depend on whether siblings were fused.
+        for name in ("packed_weights", "scales", "bias"):
+            self._non_persistent_buffers_set.add(name)
         self.split_sizes = [part.out_features for part in parts]
         self._offsets = [0]
         for size in self.split_sizes:
@@ -102,6 +106,35 @@ class FusedSlice(torch.nn.Module):
 
     def forward(self, activations: torch.Tensor) -> torch.Tensor:
         return self._owner._columns(activations, self.index)
+
+    # ---- state dict: this layer's rows under this layer's name, exactly as before fusion -------------
+    def _tensors(self) -> dict:
+        named = {"packed_weights": self.packed_weights, "scales": self.scales}
+        if self._owner.bias is not None:
+            named["bias"] = self.bias
+        return named
+
+    def _save_to_state_dict(self, destination, prefix, keep_vars):
+        for name, view in self._tensors().items():
+            destination[prefix + name] = view if keep_vars else view.detach()
+
+    def _load_from_state_dict(self, state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+        for name, view in self._tensors().items():
+            key = prefix + name
+            if key not in state_dict:
+                if strict:
+                    missing_keys.append(key)
+                continue
+            value = state_dict[key]
+            if tuple(value.shape) != tuple(view.shape) or value.dtype != view.dtype:
+                error_msgs.append(f"size mismatch for {key}: copying a param with shape {tuple(value.shape)} "
+                                  f"and dtype {value.dtype}, the layer holds {tuple(view.shape)} {view.dtype}")
+                continue
+            with torch.no_grad():
+                view.copy_(value)
+        if strict:
+            unexpected_keys.extend(key for key in state_dict
+                                   if key.startswith(prefix) and key[len(prefix):] not in self._tensors())
 
     def extra_repr(self) -> str:
         return f"in_features={self.in_features}, out_features={self.out_features}, slice={self.index} of a fused launch"

@@ -19,11 +19,17 @@ def replace_linear_layers(
     prefix: str = "",
     fused: bool = True,
     packed_only: bool = False,
+    fuse_siblings: bool | None = None,
 ) -> int:
     """Recursively replace every compatible ``nn.Linear`` below ``module``; returns how many.
 
     ``packed_only=True`` only looks at layer shapes and allocates empty packed storage (works on
     the meta device); the packed tensors are expected to arrive through ``load_state_dict``.
+
+    ``fuse_siblings`` (not in the reference): afterwards, sibling projections that read the same activations
+    (``q_proj``/``k_proj``/``v_proj``; ``gate_proj``/``up_proj``) are served by one launch over their
+    concatenated rows (``nibble_b200.fusion.fuse_parallel_linears``).  Module names, outputs and state-dict keys
+    stay what they were.  Default: on, unless the environment variable ``W4A16_FUSE_SIBLINGS`` is ``0``.
     """
     if group_size <= 0:
         raise ValueError("group_size must be greater than zero")
@@ -34,7 +40,8 @@ def replace_linear_layers(
         if isinstance(child, QuantizedLinear):
             continue
         if not isinstance(child, torch.nn.Linear):
-            replaced += replace_linear_layers(child, group_size, prefix=path, fused=fused, packed_only=packed_only)
+            replaced += replace_linear_layers(child, group_size, prefix=path, fused=fused, packed_only=packed_only,
+                                              fuse_siblings=False)
             continue
         if child.in_features % group_size:
             warnings.warn(
@@ -58,6 +65,15 @@ def replace_linear_layers(
         new.train(child.training)
         setattr(module, name, new)
         replaced += 1
+    if not prefix:   # the outermost call: every replacement below is done
+        if fuse_siblings is None:
+            import os
+
+            fuse_siblings = os.environ.get("W4A16_FUSE_SIBLINGS", "1") != "0"
+        if fuse_siblings:
+            from .fusion import fuse_parallel_linears
+
+            fuse_parallel_linears(module)
     return replaced
 
 

@@ -133,17 +133,20 @@ class RowParallelQuantizedLinear(torch.nn.Module):
 
 # ---------------------------------------------------------------------------------------------
 # Exchange fused into the kernels: a sender's epilogue stores its result straight into a buffer on
-# every rank over NVLink (peer-mapped memory) and raises a flag there; the kernel that consumes the
-# result waits for the flags in its own prologue, with its weight prefetch already in flight, and
-# gives the buffer back with a second set of flags.  No collective-library call per layer.
+# every rank over NVLink (peer-mapped memory), every element together with a tag naming the
+# publication it belongs to; the kernel that consumes the result re-reads, while it stages its
+# activations and with its weight prefetch already in flight, whatever has not arrived yet, and gives
+# the buffer back through a set of flags.  No fence, no flag round trip, no collective-library call.
 # The protocol is described beside w4a16_peer_target / w4a16_peer_source in include/w4a16_b200.h.
 # ---------------------------------------------------------------------------------------------
 import ctypes
 
 from . import _native
 
-_MAX_POLLS = 2_000_000   # bounded device-side wait: roughly a second before a missing rank is reported
-_FLAG_BYTES = 512        # published[world] at +0, consumed[world] at +256
+_MAX_POLLS = 1_000_000   # bounded device-side wait: about a second before a missing rank is reported
+_FLAG_BYTES = 256        # consumed[world]
+_HALF_ELEMENT = 4        # bytes of a tagged FP16 element in a result buffer
+_FLOAT_ELEMENT = 8       # bytes of a tagged FP32 element
 
 
 def _stream_ptr() -> ctypes.c_void_p:
@@ -172,8 +175,8 @@ class LocalRanks:
 
 
 class PeerRegion:
-    """Memory of one sharded layer on this rank: ``[result buffer 0 | result buffer 1 | published[world] |
-    consumed[world]]`` in memory every rank can write (torch symmetric memory, or plain tensors with
+    """Memory of one sharded layer on this rank: ``[result buffer 0 | result buffer 1 | consumed[world]]``
+    in memory every rank can write (torch symmetric memory, or plain tensors with
     ``LocalRanks``), plus this rank's private words (done, send epoch, staged, status)."""
 
     def __init__(self, result_bytes: int, process_group=None, *, local: LocalRanks | None = None, rank: int | None = None,
@@ -204,8 +207,7 @@ class PeerRegion:
             raise ValueError("at most 32 ranks")
         flags0 = 2 * self.result_bytes
         i64 = dict(dtype=torch.int64, device=device)
-        self._published_table = torch.tensor([p + flags0 for p in self.peer_base], **i64)
-        self._consumed_table = torch.tensor([p + flags0 + 256 for p in self.peer_base], **i64)
+        self._consumed_table = torch.tensor([p + flags0 for p in self.peer_base], **i64)
         self.counters = torch.zeros(4, dtype=torch.int32, device=device)   # done, send epoch, staged, status
         self._tables: dict = {}
 
@@ -225,15 +227,13 @@ class PeerRegion:
         return self._tables[byte_offset]
 
     def target(self, byte_offset: int, ld: int, column_offset: int) -> _native.PeerTarget:
-        return _native.PeerTarget(self.out_table(byte_offset).data_ptr(), self._published_table.data_ptr(),
-                                  self.base + 2 * self.result_bytes + 256, self._counter(0), self._counter(1),
-                                  self._counter(3), self.result_bytes, ld, column_offset, self.max_polls, self.rank,
-                                  self.world)
+        return _native.PeerTarget(self.out_table(byte_offset).data_ptr(), self.base + 2 * self.result_bytes,
+                                  self._counter(0), self._counter(1), self._counter(3), self.result_bytes, ld,
+                                  column_offset, self.max_polls, self.rank, self.world)
 
-    def source(self) -> _native.PeerSource:
-        return _native.PeerSource(self._counter(1), self.base + 2 * self.result_bytes, self._consumed_table.data_ptr(),
-                                  self._counter(2), self._counter(3), self.result_bytes, self.max_polls, self.rank,
-                                  self.world)
+    def source(self, first_column: int = 0, columns_per_rank: int = 0) -> _native.PeerSource:
+        return _native.PeerSource(self._counter(1), self._consumed_table.data_ptr(), self._counter(2), self._counter(3),
+                                  self.result_bytes, self.max_polls, first_column, columns_per_rank, self.rank, self.world)
 
     def check(self) -> None:
         """Host-side health check (synchronises): raises if a bounded wait gave up on some rank."""
@@ -261,7 +261,10 @@ class PeerView:
 
     @property
     def data_ptr(self) -> int:
-        return self.region.base + 2 * self.column0
+        return self.region.base + _HALF_ELEMENT * self.column0
+
+    def source(self) -> _native.PeerSource:
+        return self.region.source(self.column0, self.ld // self.region.world)
 
     def materialize(self) -> torch.Tensor:
         if self.column0 or self.columns != self.ld:
@@ -269,9 +272,9 @@ class PeerView:
         if (self.rows * self.ld) % 8:
             raise ValueError("rows * columns must be a multiple of 8")
         out = torch.empty((self.rows, self.ld), dtype=torch.float16, device=self.region.buffer.device)
-        source = self.region.source()
+        source = self.source()
         status = _native.core().w4a16_wait_peers(ctypes.byref(source), self.region.base, out.data_ptr(),
-                                                 out.numel() * 2, _launch_flags(), _stream_ptr())
+                                                 out.numel(), _launch_flags(), _stream_ptr())
         if status != 0:
             raise RuntimeError(f"w4a16_wait_peers failed: {_native.status_string(status)}")
         return out
@@ -287,7 +290,7 @@ def _launch_peer_linear(layer: QuantizedLinear, x, m: int, workspaces: dict, tar
     if isinstance(x, PeerView):
         if x.columns != layer.in_features or x.rows != m:
             raise ValueError("the view's shape does not match the layer")
-        x_ptr, x_ld, source = x.data_ptr, x.ld, x.region.source()
+        x_ptr, x_ld, source = x.data_ptr, x.ld, x.source()
         device = x.region.buffer.device
     else:
         if x.dtype != torch.float16 or x.ndim != 2 or x.shape[1] != layer.in_features or x.stride(1) != 1:
@@ -327,7 +330,7 @@ class PeerColumnParallelQuantizedLinear(torch.nn.Module):
         self.local = QuantizedLinear(packed_shard, scales_shard, group_size)
         n_local = self.local.out_features
         world = local.world if local is not None else dist.get_world_size(process_group)
-        self.region = PeerRegion(max_rows * n_local * world * 2, process_group, local=local, rank=rank, key=name,
+        self.region = PeerRegion(max_rows * n_local * world * _HALF_ELEMENT, process_group, local=local, rank=rank, key=name,
                                  max_polls=max_polls)
         self.max_rows = max_rows
         self.in_features = self.local.in_features
@@ -371,7 +374,7 @@ class PeerRowParallelQuantizedLinear(torch.nn.Module):
         self.local = QuantizedLinear(packed_shard, scales_shard, group_size)
         world = local.world if local is not None else dist.get_world_size(process_group)
         n = self.local.out_features
-        self.region = PeerRegion(world * max_rows * n * 4, process_group, local=local, rank=rank, key=name,
+        self.region = PeerRegion(world * max_rows * n * _FLOAT_ELEMENT, process_group, local=local, rank=rank, key=name,
                                  max_polls=max_polls)
         self.max_rows = max_rows
         self.in_features = self.local.in_features
@@ -383,7 +386,7 @@ class PeerRowParallelQuantizedLinear(torch.nn.Module):
         if m > self.max_rows:
             raise ValueError(f"batch of {m} rows exceeds max_rows={self.max_rows}")
         region, n = self.region, self.out_features
-        target = region.target(region.rank * m * n * 4, n, 0)   # my slot on every rank
+        target = region.target(region.rank * m * n * _FLOAT_ELEMENT, n, 0)   # my slot on every rank
         _launch_peer_linear(self.local, x, m, self._workspace, target, out_f32=True)
         return m
 

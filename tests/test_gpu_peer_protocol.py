@@ -2,9 +2,9 @@
 w4a16_peer_target / w4a16_peer_source) with all ranks of a sharded layer emulated in one process.
 
 The ranks' kernels run one after the other on one stream (``LocalRanks``): every rank's senders are launched
-before any rank's readers, so no kernel ever waits for a kernel that has not run.  What is covered: the two
-result buffers alternating by publication number, readers inside the consuming linear (wait, parity offset,
-release), the reader kernels (``materialize``, ``finish``), column slices as inputs, and -- with a rank that never
+before any rank's readers, so no kernel ever waits for a kernel that has not run.  What is covered: tagged
+elements, the two result buffers alternating by publication number, readers inside the consuming linear (re-reading
+what has not arrived, parity offset, release), the reader kernels (``materialize``, ``finish``), column slices as inputs, and -- with a rank that never
 launches -- every bounded wait running out: the call returns, the status word names the missing rank, and the
 GPU goes on working.  Nothing here hangs, traps or faults by design.
 """
@@ -28,11 +28,13 @@ def _layer(n, k, seed):
     return packed.cuda(), scales.cuda()
 
 
-def _result(region, epoch, rows, ld, dtype=torch.float16):
-    """The result buffer that publication `epoch` went to, as a [rows, ld] tensor."""
+def _result(region, epoch, rows, ld):
+    """The FP16 result of publication `epoch` as a [rows, ld] tensor, decoded from the tagged elements of the
+    result buffer it went to (value in the low half of each 32-bit word, tag 0x8000 | epoch in the high half)."""
     start = (epoch & 1) * region.result_bytes
-    size = rows * ld * (2 if dtype == torch.float16 else 4)
-    return region.buffer[start:start + size].view(dtype).view(rows, ld)
+    words = region.buffer[start:start + rows * ld * 4].view(torch.int32).view(rows, ld)
+    assert bool((((words >> 16) & 0xFFFF) == (0x8000 | (epoch & 0x7FFF))).all()), "an element carries the wrong tag"
+    return (words & 0xFFFF).to(torch.int16).view(torch.float16)
 
 
 @pytest.mark.parametrize("world", [1, 2, 4])
