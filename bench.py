@@ -450,7 +450,7 @@ def decode_bench(torch, device) -> dict:
     saved_pdl = os.environ.pop("W4A16_PDL", None)
     torch.cuda.reset_peak_memory_stats(device)
     out["fp16_cublas"] = measure("fp16")
-    replaced = replace_linear_layers(model, group_size=GROUP)
+    replaced = replace_linear_layers(model, group_size=GROUP, fuse_siblings=False)   # fused further down, to show both
     out["linears_replaced"] = replaced
     torch.cuda.empty_cache()
     torch.cuda.reset_peak_memory_stats(device)

@@ -90,23 +90,11 @@ def save_quantized_model_checkpoint(path: str | os.PathLike, model: torch.nn.Mod
     """Write the state dict of a model whose linears are already ``QuantizedLinear`` (CPU tensors, the
     reference's keys ``format``, ``version``, ``source_model``, ``group_size``, ``state_dict``).
 
-    Layers fused by ``fuse_parallel_linears`` are written under their original names, slice by slice,
-    so the file does not depend on whether fusion was applied.
+    Layers fused by ``fuse_parallel_linears`` appear under their original names (each slice saves its own
+    rows), so the file does not depend on whether fusion was applied.
     """
-    from .fusion import FusedQuantizedLinear, FusedSlice
-
-    state = {}
-    fused_prefixes = tuple(name + "." for name, module in model.named_modules() if isinstance(module, FusedQuantizedLinear))
-    for key, tensor in model.state_dict().items():
-        if fused_prefixes and key.startswith(fused_prefixes):
-            continue
-        state[key] = tensor.detach().cpu()
-    for name, module in model.named_modules():
-        if isinstance(module, FusedSlice):
-            state[f"{name}.packed_weights"] = module.packed_weights.detach().cpu().clone()
-            state[f"{name}.scales"] = module.scales.detach().cpu().clone()
-            if module.bias is not None:
-                state[f"{name}.bias"] = module.bias.detach().cpu().clone()
+    # FusedSlice modules save their own rows under their own names, so the model's state dict already is the file's
+    state = {key: tensor.detach().cpu().clone() for key, tensor in model.state_dict().items()}
     os.makedirs(os.path.dirname(os.path.abspath(os.fspath(path))), exist_ok=True)
     torch.save({"format": MODEL_FORMAT_NAME, "version": MODEL_FORMAT_VERSION, "source_model": source_model,
                 "group_size": int(group_size), "state_dict": state}, os.fspath(path))
@@ -168,7 +156,7 @@ def load_packed_model(model: torch.nn.Module, path: str | os.PathLike, device: s
     if world is None:
         world = dist.get_world_size(process_group)
     state = dict(checkpoint["state_dict"])
-    replaced = replace_linear_layers(model, group_size=group_size, fused=fused, packed_only=True)
+    replaced = replace_linear_layers(model, group_size=group_size, fused=fused, packed_only=True, fuse_siblings=False)
 
     # Take the planned layers out of the tree before it is materialised, so that their full-size packed
     # storage is never allocated on the device; remember where they sat.

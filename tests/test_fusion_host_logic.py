@@ -29,7 +29,7 @@ class Block(torch.nn.Module):
 def _quantised_block(bias=False, seed=0):
     torch.manual_seed(seed)
     block = Block(bias=bias).half()
-    assert replace_linear_layers(block, group_size=128) == 7
+    assert replace_linear_layers(block, group_size=128, fuse_siblings=False) == 7
     return block
 
 
@@ -60,8 +60,9 @@ def test_slices_expose_the_original_layers_tensors_and_bias_is_carried():
     assert torch.equal(block.k_proj.scales, k_scales)
     assert torch.equal(block.k_proj.bias, k_bias)
     keys = set(block.state_dict())
-    assert "q_proj__k_proj__v_proj.packed_weights" in keys and "q_proj__k_proj__v_proj.bias" in keys
-    assert not any(key.startswith("q_proj.") for key in keys)
+    # the state dict keeps the layers' own names; the concatenated tensors are not saved a second time
+    assert {"q_proj.packed_weights", "k_proj.scales", "v_proj.bias", "up_proj.packed_weights"} <= keys
+    assert not any(key.startswith("q_proj__k_proj__v_proj.") for key in keys)
 
 
 def test_cache_follows_tensor_identity_and_version(oracle_backend):
@@ -100,3 +101,34 @@ def test_inference_mode_tensors_are_cached_by_identity(oracle_backend):
         block.gate_proj(x)
         block.up_proj(x)
     assert block.gate_proj__up_proj.launches == 1
+
+
+def test_replacement_fuses_siblings_by_default_and_keeps_names_and_state_dict(oracle_backend, monkeypatch):
+    torch.manual_seed(5)
+    plain = Block(bias=True).half()
+    fused = Block(bias=True).half()
+    fused.load_state_dict(plain.state_dict())
+    assert replace_linear_layers(plain, group_size=128, fuse_siblings=False) == 7
+    assert replace_linear_layers(fused, group_size=128) == 7          # default: siblings share a launch
+    assert isinstance(fused.q_proj, FusedSlice) and isinstance(fused.gate_proj, FusedSlice)
+    assert type(fused.o_proj) is QuantizedLinear and type(plain.q_proj) is QuantizedLinear
+    want, got = plain.state_dict(), fused.state_dict()
+    assert list(got) == list(want)                                    # same keys, same order
+    for key in want:
+        assert torch.equal(got[key], want[key]), key
+    x = torch.randn((2, 128), generator=torch.Generator().manual_seed(1)).half()
+    del oracle_backend[:]
+    assert torch.equal(fused(x), plain(x))
+    assert len(oracle_backend) == 4 + 7
+    # a state dict written by either loads into the other
+    other = Block(bias=True).half()
+    replace_linear_layers(other, group_size=128)
+    other.load_state_dict(want)
+    assert torch.equal(other(x), plain(x))
+    plain.load_state_dict(other.state_dict())
+    with __import__("pytest").raises(RuntimeError, match="size mismatch"):
+        other.load_state_dict({**want, "k_proj.scales": want["k_proj.scales"][:1]})
+    monkeypatch.setenv("W4A16_FUSE_SIBLINGS", "0")
+    unfused = Block().half()
+    replace_linear_layers(unfused, group_size=128)
+    assert type(unfused.q_proj) is QuantizedLinear

@@ -135,7 +135,7 @@ def test_fused_siblings_one_launch_same_numbers():
 
     torch.manual_seed(4)
     attn = Attn().half().cuda()
-    assert replace_linear_layers(attn, group_size=128) == 3
+    assert replace_linear_layers(attn, group_size=128, fuse_siblings=False) == 3
     x = torch.randn((1, 1, 2048), dtype=torch.float16, device="cuda")
     separate = [t.clone() for t in attn(x)]
     packed = [m.packed_weights.clone() for m in (attn.q_proj, attn.k_proj, attn.v_proj)]
