@@ -356,7 +356,7 @@ def cpu_baseline_leg(blocks: int, repeats: int) -> dict:
     return json.loads(proc.stdout.strip().splitlines()[-1])["cpu_baseline"]
 
 
-def decode_bench(torch, device) -> dict:
+def decode_bench(torch, device, runners_only: bool = False) -> dict:
     """Decode tokens/s of a TinyLlama-1.1B-shaped model (random weights), FP16 cuBLAS vs W4A16.
 
     Protocol of the reference's scripts/generate.py:307-365: batch 1, 16-token prompt of seeded
@@ -449,30 +449,34 @@ def decode_bench(torch, device) -> dict:
     out = {"model": "TinyLlama-1.1B architecture, random weights", "prompt_tokens": prompt_len, "new_tokens": new_tokens}
     saved_pdl = os.environ.pop("W4A16_PDL", None)
     torch.cuda.reset_peak_memory_stats(device)
-    out["fp16_cublas"] = measure("fp16")
+    if not runners_only:
+        out["fp16_cublas"] = measure("fp16")
     replaced = replace_linear_layers(model, group_size=GROUP, fuse_siblings=False)   # fused further down, to show both
     out["linears_replaced"] = replaced
     torch.cuda.empty_cache()
     torch.cuda.reset_peak_memory_stats(device)
-    out["w4a16"] = measure("w4a16")
-    os.environ["W4A16_PDL"] = "1"
-    out["w4a16_programmatic_launch"] = measure("w4a16+pdl")
     from nibble_b200 import fuse_parallel_linears
 
+    if not runners_only:
+        out["w4a16"] = measure("w4a16")
+        os.environ["W4A16_PDL"] = "1"
+        out["w4a16_programmatic_launch"] = measure("w4a16+pdl")
     out["launches_fused"] = fuse_parallel_linears(model)     # q/k/v -> one launch, gate/up -> one launch per block
     torch.cuda.empty_cache()
-    # with every fused launch sitting between two torch kernels there is no chain of our own kernels left
-    # for programmatic launch to overlap, and the attribute costs time: measured both ways
-    out["w4a16_programmatic_launch_fused_qkv_gate_up"] = measure("w4a16+pdl+fused q/k/v, gate/up")
+    if not runners_only:
+        # with every fused launch sitting between two torch kernels there is no chain of our own kernels left
+        # for programmatic launch to overlap, and the attribute costs time: measured both ways
+        out["w4a16_programmatic_launch_fused_qkv_gate_up"] = measure("w4a16+pdl+fused q/k/v, gate/up")
+        os.environ.pop("W4A16_PDL", None)
+        out["w4a16_fused_qkv_gate_up"] = measure("w4a16+fused q/k/v, gate/up")
     os.environ.pop("W4A16_PDL", None)
-    out["w4a16_fused_qkv_gate_up"] = measure("w4a16+fused q/k/v, gate/up")
 
     # this package's own decode step (nibble_b200/decode.py): same protocol, the prompt is consumed one
     # token per step, so "prefill" here is 16 decode steps
     from nibble_b200.decode import LlamaDecodeRunner
 
-    def measure_runner(label: str, fuse_inputs: bool = True) -> dict:
-        runner = LlamaDecodeRunner(model, max_len=prompt_len + new_tokens + 8, fuse_inputs=fuse_inputs)
+    def measure_runner(label: str, fuse_inputs: bool = True, persistent: bool = False) -> dict:
+        runner = LlamaDecodeRunner(model, max_len=prompt_len + new_tokens + 8, fuse_inputs=fuse_inputs, persistent=persistent)
         ids = prompt.reshape(-1)
 
         def generate():
@@ -496,17 +500,21 @@ def decode_bench(torch, device) -> dict:
         decode_ms = total_ms - prefill_ms
         row = {"decode_tok_s": round((new_tokens - 1) / decode_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
                "ms_per_token": round(decode_ms / (new_tokens - 1), 4), "e2e_tok_s": round(new_tokens / total_ms * 1e3, 1),
-               "mode": "cuda_graph, own decode step", "kernels_per_token": runner.launches_per_step + 1,
-               "cache_overrun": int(runner.status.item())}
+               "mode": "one cooperative launch per token" if persistent else "cuda_graph, own decode step",
+               "kernels_per_token": runner.launches_per_step + (0 if persistent else 1),
+               "cache_overrun": int(runner.status.item()),
+               "step_status": int(runner.step_status.item()) if persistent else 0}
         log(f"  decode {label}: {row}")
         return row
 
     try:
-        out["w4a16_decode_runner_separate_norm_and_silu_kernels"] = measure_runner("w4a16 decode runner, separate norm/silu kernels", False)
-        out["w4a16_decode_runner"] = measure_runner("w4a16 decode runner")
+        if not runners_only:
+            out["w4a16_decode_runner_separate_norm_and_silu_kernels"] = measure_runner("w4a16 decode runner, separate norm/silu kernels", False)
+            out["w4a16_decode_runner"] = measure_runner("w4a16 decode runner")
         os.environ["W4A16_PDL"] = "1"
         out["w4a16_decode_runner_programmatic_launch"] = measure_runner("w4a16 decode runner+pdl")
         os.environ.pop("W4A16_PDL", None)
+        out["w4a16_decode_runner_persistent"] = measure_runner("w4a16 decode runner, one persistent launch", persistent=True)
     except Exception as error:
         os.environ.pop("W4A16_PDL", None)
         out["w4a16_decode_runner"] = {"error": repr(error)[:300]}
@@ -1264,7 +1272,7 @@ def main() -> None:
     parser.add_argument("--quick", action="store_true", help="skip the per-shape tables")
     parser.add_argument("--kernel-only", action="store_true",
                         help="only the timed region (bracketed by cudaProfilerStart/Stop), for profiler runs")
-    parser.add_argument("--workload", choices=["tinyllama_decode_linears_m1", "llama70b_tp", "decode_step"],
+    parser.add_argument("--workload", choices=["tinyllama_decode_linears_m1", "llama70b_tp", "decode_step", "decode"],
                         default="tinyllama_decode_linears_m1")
     parser.add_argument("--batch", type=int, default=1, help="M for --workload llama70b_tp")
     parser.add_argument("--cpu-blocks", type=int, default=1,
@@ -1278,6 +1286,11 @@ def main() -> None:
         result = run_single_layer(args)
     elif args.workload == "decode_step" and args.impl == "product":
         result = run_decode_step(args)
+    elif args.workload == "decode" and args.impl == "product":
+        import torch
+
+        torch.cuda.set_device(0)
+        result = {"workload": "decode", "decode": decode_bench(torch, torch.device("cuda", 0), runners_only=args.quick)}
     elif args.workload == "llama70b_tp" and args.impl == "product":
         result = run_tensor_parallel(args)
     else:

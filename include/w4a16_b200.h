@@ -273,6 +273,65 @@ int w4a16_attention_decode_f16(const void* qkv, void* k_cache, void* v_cache, vo
                                float softmax_scale, uint32_t* status, uint32_t flags, w4a16_stream_t stream);
 
 /*
+ * One whole decode step (batch 1) of a LLaMA-architecture model as ONE cooperative kernel launch: resident
+ * CTAs walk a prebuilt list of operations (per block: fused q/k/v with add + RMSNorm inside, attention, o_proj,
+ * fused gate/up with add + RMSNorm inside, down_proj with SiLU * up inside; then lm_head with the final norm and
+ * the arg-max), handing over between operations through one counter in L2 instead of a kernel boundary, the next
+ * operation's weights already being fetched while the hand-off is waited for.  Same arithmetic as the kernels
+ * above.  No counterpart in the reference (it drives HuggingFace's generate(), scripts/generate.py:260-365).
+ *
+ * The caller describes the model once (device pointers; q/k/v and gate/up packed as single matrices: rows
+ * [q | k | v] and [gate | up]; all group size 128; hidden, intermediate and q_heads * head_dim multiples of 256;
+ * head_dim 64 or 128; KV caches [kv_heads][max_len][head_dim] per layer), provides w4a16_decode_plan_bytes()
+ * bytes of 256-byte aligned device memory, and builds the plan (this copies the operation list to the device and
+ * synchronises `stream`).  The plan also holds the step's work buffers.  `token` and `position` are device
+ * scalars: a step consumes *token at *position, appends to the caches, leaves the greedy next token in *token and
+ * adds 1 to *position.  info->logits (FP16 [vocab]) and info->status (uint32: 0 healthy, 1 the position was outside
+ * the cache, 0x100 + n: the hand-off before operation n was not seen within its poll limit -- the step still ends)
+ * point into the plan.  Steps on one plan must be ordered on one stream.
+ */
+typedef struct w4a16_decode_layer {
+    const void* norm1;            /* input_layernorm weight, FP16 [hidden]                         */
+    const void* qkv_packed;       /* [(q_heads + 2 kv_heads) * head_dim, hidden / 2]                */
+    const void* qkv_scales;
+    const void* o_packed;         /* [hidden, q_heads * head_dim / 2]                              */
+    const void* o_scales;
+    const void* norm2;            /* post_attention_layernorm weight                               */
+    const void* gate_up_packed;   /* [2 * intermediate, hidden / 2]                                */
+    const void* gate_up_scales;
+    const void* down_packed;      /* [hidden, intermediate / 2]                                    */
+    const void* down_scales;
+    void* k_cache;
+    void* v_cache;
+} w4a16_decode_layer;
+
+typedef struct w4a16_decode_model {
+    int32_t layers, hidden, q_heads, kv_heads, head_dim, intermediate, vocab, max_len;
+    float eps, rope_scale, softmax_scale;
+    const void* embed;            /* FP16 [vocab, hidden]                                          */
+    const void* final_norm;
+    const void* lm_head_packed;   /* [vocab, hidden / 2]                                           */
+    const void* lm_head_scales;
+    const float* inv_freq;        /* [head_dim / 2]                                                */
+    const w4a16_decode_layer* layer;   /* HOST array of `layers` entries                           */
+} w4a16_decode_model;
+
+typedef struct w4a16_decode_plan_info {
+    const void* logits;
+    const void* status;
+    int32_t operations;
+    int32_t grid;
+    int32_t head_dim;
+    uint32_t smem_bytes;
+} w4a16_decode_plan_info;
+
+size_t w4a16_decode_plan_bytes(const w4a16_decode_model* model);   /* 0 when the model does not fit the kernel */
+int w4a16_decode_plan_build(const w4a16_decode_model* model, void* plan, size_t plan_bytes,
+                            int64_t* token, int64_t* position, w4a16_decode_plan_info* info,
+                            w4a16_stream_t stream);
+int w4a16_decode_step_f16(void* plan, const w4a16_decode_plan_info* info, w4a16_stream_t stream);
+
+/*
  * w4a16_linear_f16 for callers that cannot allocate device memory (no cudaMalloc after start-up,
  * no workspace handed to a plugin, an open stream capture): the split-K scratch is a fixed array
  * inside the library's device image, w4a16_static_scratch_bytes() bytes per GPU, instead of a

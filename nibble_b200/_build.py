@@ -26,7 +26,7 @@ OBJ = PKG / "build"
 CORE_LIB = PKG / "libw4a16_b200.so"
 TORCH_LIB = PKG / "_C.so"
 
-CUDA_SOURCES = ["capi.cu", "linear_mma.cu", "linear_generic.cu", "dequantize.cu", "linear_static_scratch.cu", "linear_tcgen05.cu", "quantize.cu", "decode_ops.cu"]
+CUDA_SOURCES = ["capi.cu", "linear_mma.cu", "linear_generic.cu", "dequantize.cu", "linear_static_scratch.cu", "linear_tcgen05.cu", "quantize.cu", "decode_ops.cu", "decode_persistent.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++20", "-lineinfo",

@@ -63,6 +63,31 @@ class PeerSource(ctypes.Structure):
     ]
 
 
+class DecodeLayer(ctypes.Structure):
+    """``w4a16_decode_layer``: device pointers of one decoder block."""
+
+    _fields_ = [(name, ctypes.c_void_p) for name in (
+        "norm1", "qkv_packed", "qkv_scales", "o_packed", "o_scales", "norm2", "gate_up_packed", "gate_up_scales",
+        "down_packed", "down_scales", "k_cache", "v_cache")]
+
+
+class DecodeModel(ctypes.Structure):
+    """``w4a16_decode_model``."""
+
+    _fields_ = [(name, ctypes.c_int32) for name in (
+        "layers", "hidden", "q_heads", "kv_heads", "head_dim", "intermediate", "vocab", "max_len")] + [
+        ("eps", ctypes.c_float), ("rope_scale", ctypes.c_float), ("softmax_scale", ctypes.c_float),
+        ("embed", ctypes.c_void_p), ("final_norm", ctypes.c_void_p), ("lm_head_packed", ctypes.c_void_p),
+        ("lm_head_scales", ctypes.c_void_p), ("inv_freq", ctypes.c_void_p), ("layer", ctypes.POINTER(DecodeLayer))]
+
+
+class DecodePlanInfo(ctypes.Structure):
+    """``w4a16_decode_plan_info``."""
+
+    _fields_ = [("logits", ctypes.c_void_p), ("status", ctypes.c_void_p), ("operations", ctypes.c_int32),
+                ("grid", ctypes.c_int32), ("head_dim", ctypes.c_int32), ("smem_bytes", ctypes.c_uint32)]
+
+
 _P = ctypes.c_void_p
 _I = ctypes.c_int64
 
@@ -96,6 +121,10 @@ C_API = {
         [_P, _P, _P, _P, _P, _P, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_float,
          ctypes.c_float, _P, ctypes.c_uint32, _P],
     ),
+    "w4a16_decode_plan_bytes": (ctypes.c_size_t, [ctypes.POINTER(DecodeModel)]),
+    "w4a16_decode_plan_build": (ctypes.c_int, [ctypes.POINTER(DecodeModel), _P, ctypes.c_size_t, _P, _P,
+                                               ctypes.POINTER(DecodePlanInfo), _P]),
+    "w4a16_decode_step_f16": (ctypes.c_int, [_P, ctypes.POINTER(DecodePlanInfo), _P]),
     "w4a16_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32)]),
     "w4a16_launch_count": (ctypes.c_uint64, []),
     "w4a16_status_string": (ctypes.c_char_p, [ctypes.c_int]),

@@ -276,6 +276,19 @@ int w4a16_argmax_advance_f16(const void* logits, int64_t count, int64_t* token, 
                                         (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0, reinterpret_cast<cudaStream_t>(stream));
 }
 
+size_t w4a16_decode_plan_bytes(const w4a16_decode_model* model) { return w4a16::decode_plan_bytes(model); }
+
+int w4a16_decode_plan_build(const w4a16_decode_model* model, void* plan, size_t plan_bytes, int64_t* token,
+                            int64_t* position, w4a16_decode_plan_info* info, w4a16_stream_t stream) {
+    return w4a16::decode_plan_build(model, plan, plan_bytes, token, position, info, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int w4a16_decode_step_f16(void* plan, const w4a16_decode_plan_info* info, w4a16_stream_t stream) {
+    if (plan == nullptr || info == nullptr) return W4A16_ERR_NULL_POINTER;
+    return w4a16::launch_decode_step(plan, info->operations, info->grid, info->head_dim, info->smem_bytes,
+                                     reinterpret_cast<cudaStream_t>(stream));
+}
+
 int w4a16_attention_decode_f16(const void* qkv, void* k_cache, void* v_cache, void* out, const int64_t* position,
                                const float* inv_freq, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_len,
                                float rope_scale, float softmax_scale, uint32_t* status, uint32_t flags,

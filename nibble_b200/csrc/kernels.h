@@ -74,6 +74,12 @@ int launch_attention_decode(const __half* qkv, __half* k_cache, __half* v_cache,
                             const float* inv_freq, int q_heads, int kv_heads, int head_dim, int max_len, float rope_scale,
                             float softmax_scale, unsigned* status, bool programmatic, cudaStream_t stream);
 
+// One decode step as one cooperative launch over a prebuilt plan (decode_persistent.cu).
+size_t decode_plan_bytes(const w4a16_decode_model* model);
+int decode_plan_build(const w4a16_decode_model* model, void* plan, size_t plan_bytes, int64_t* token, int64_t* position,
+                      w4a16_decode_plan_info* info, cudaStream_t stream);
+int launch_decode_step(const void* plan, int32_t n_ops, int32_t grid, int32_t head_dim, uint32_t smem_bytes, cudaStream_t stream);
+
 // Quantise + pack on the device (quantize.cu): FP16 or FP32 weights -> packed codes and FP16 scales.
 int launch_quantize_pack(const void* weights, bool is_f32, uint8_t* packed, __half* scales, int64_t N, int64_t K,
                          int64_t group, cudaStream_t stream);

@@ -109,7 +109,7 @@ class LlamaDecodeRunner:
     captures the step in a CUDA graph at the first ``step``.
     """
 
-    def __init__(self, model: torch.nn.Module, max_len: int, fuse_inputs: bool | None = None):
+    def __init__(self, model: torch.nn.Module, max_len: int, fuse_inputs: bool | None = None, persistent: bool = False):
         config = model.config
         self.model = model
         self.hidden = config.hidden_size
@@ -171,6 +171,46 @@ class LlamaDecodeRunner:
             self.down_out = torch.zeros((1, self.hidden), **half)
             self.logits = torch.zeros((1, self.lm_head.out_features), **half)
             self.workspace = torch.zeros((8 << 20,), dtype=torch.uint8, device=device)   # split-K scratch; kernels leave it zeroed
+        self.persistent = bool(persistent)
+        if self.persistent:
+            if not self.fuse_inputs:
+                raise ValueError("the persistent step needs bias-free QuantizedLinear layers with group_size 128")
+            self._build_plan()
+
+    # ------------------------------------------------------------------ the whole step as one cooperative launch
+    def _build_plan(self) -> None:
+        lib = _native.core()
+        layers = (_native.DecodeLayer * len(self.layers))()
+        for index, entry in enumerate(self.layers):
+            layers[index] = _native.DecodeLayer(
+                entry["norm1"].data_ptr(), entry["qkv"].packed_weights.data_ptr(), entry["qkv"].scales.data_ptr(),
+                entry["o"].packed_weights.data_ptr(), entry["o"].scales.data_ptr(), entry["norm2"].data_ptr(),
+                entry["gate_up"].packed_weights.data_ptr(), entry["gate_up"].scales.data_ptr(),
+                entry["down"].packed_weights.data_ptr(), entry["down"].scales.data_ptr(),
+                self.k_cache[index].data_ptr(), self.v_cache[index].data_ptr())
+        model = _native.DecodeModel(
+            len(self.layers), self.hidden, self.q_heads, self.kv_heads, self.head_dim, self.inter, self.lm_head.out_features,
+            self.max_len, self.eps, self.rope_scale, self.head_dim ** -0.5, self.embed.data_ptr(), self.final_norm.data_ptr(),
+            self.lm_head.packed_weights.data_ptr(), self.lm_head.scales.data_ptr(), self.inv_freq.data_ptr(), layers)
+        need = lib.w4a16_decode_plan_bytes(ctypes.byref(model))
+        if need == 0:
+            raise ValueError("this model's shape does not fit the persistent decode step")
+        self._plan = torch.zeros((need,), dtype=torch.uint8, device=self.embed.device)
+        self._plan_info = _native.DecodePlanInfo()
+        _check(lib.w4a16_decode_plan_build(ctypes.byref(model), self._plan.data_ptr(), need, self.token.data_ptr(),
+                                           self.position.data_ptr(), ctypes.byref(self._plan_info),
+                                           ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "decode_plan_build")
+        base = self._plan.data_ptr()
+        vocab = self.lm_head.out_features
+        offset = self._plan_info.logits - base
+        self.logits = self._plan[offset:offset + 2 * vocab].view(torch.float16).view(1, vocab)
+        offset = self._plan_info.status - base
+        self.step_status = self._plan[offset:offset + 4].view(torch.int32)
+        self.launches_per_step = 1
+
+    def _persistent_step(self) -> None:
+        _check(_native.core().w4a16_decode_step_f16(self._plan.data_ptr(), ctypes.byref(self._plan_info),
+                                                    ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "decode_step")
 
     # ------------------------------------------------------------------ one token
     def _norm_into(self, source: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
@@ -216,6 +256,9 @@ class LlamaDecodeRunner:
 
     def step(self) -> None:
         """Consumes ``self.token`` at ``self.position``; leaves the greedy next token in ``self.token``."""
+        if self.persistent:
+            self._persistent_step()
+            return
         with torch.inference_mode():
             if self._graph is None:
                 keep = (self.token.clone(), self.position.clone(), self.k_cache.clone(), self.v_cache.clone())
@@ -236,6 +279,8 @@ class LlamaDecodeRunner:
     def reset(self) -> None:
         self.position.zero_()
         self.status.zero_()
+        if self.persistent:
+            self.step_status.zero_()
 
     # Prompts up to this many tokens are cheaper one decode step at a time than through the framework's
     # batched forward (about half a millisecond per token against a fixed ~12 ms).
@@ -280,4 +325,8 @@ class LlamaDecodeRunner:
                 self.step()
         if int(self.status.item()) != 0:
             raise RuntimeError("a decode step ran past the end of the KV cache")
+        if self.persistent and int(self.step_status.item()) != 0:
+            code = int(self.step_status.item())
+            raise RuntimeError("a decode step ran past the end of the KV cache" if code == 1 else
+                               f"the persistent decode step gave up waiting before operation {code - 0x100}")
         return out

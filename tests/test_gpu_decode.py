@@ -198,6 +198,46 @@ def test_runner_logits_follow_the_framework_forward():
         assert runner.launches_per_step == per_block * 3 + tail     # our kernels per token
         assert worst < 2e-2, worst
         assert runner.status.item() == 0
+        graph_cache = (runner.k_cache.clone(), runner.v_cache.clone())
+    # the same step as ONE cooperative launch walking a list of operations: same logits, same caches
+    runner = LlamaDecodeRunner(model, max_len=32, persistent=True)
+    worst = 0.0
+    for t in range(tokens.numel()):
+        runner.token.copy_(tokens[t:t + 1])
+        runner.step()
+        got = runner.logits[0].float()
+        scale = want[t].abs().max().item()
+        worst = max(worst, (got - want[t]).abs().max().item() / scale)
+        assert int(runner.position.item()) == t + 1
+        assert int(runner.token.item()) == int(got.argmax().item())
+    assert runner.launches_per_step == 1
+    assert int(runner.step_status.item()) == 0
+    assert worst < 2e-2, worst
+    # the launch shapes differ from the graph runner's, so sums are taken in another order: close, not equal
+    torch.testing.assert_close(runner.v_cache, graph_cache[1], rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(runner.k_cache, graph_cache[0], rtol=2e-2, atol=2e-2)
+    assert torch.equal(runner.v_cache[0], graph_cache[1][0]) or (runner.v_cache[0] == graph_cache[1][0]).float().mean().item() > 0.9
+
+
+def test_persistent_step_reports_a_full_cache_and_keeps_running():
+    from nibble_b200 import replace_linear_layers
+    from nibble_b200.decode import LlamaDecodeRunner
+
+    cfg = _config(num_hidden_layers=2)
+    torch.manual_seed(3)
+    with torch.device("cuda"):
+        model = transformers.AutoModelForCausalLM.from_config(cfg, dtype=torch.float16)
+    model.eval()
+    replace_linear_layers(model, group_size=128)
+    runner = LlamaDecodeRunner(model, max_len=8, persistent=True)
+    reference = LlamaDecodeRunner(model, max_len=8)
+    prompt = torch.tensor([7, 1, 300])
+    assert torch.equal(runner.generate(prompt, 5), reference.generate(prompt, 5))
+    assert torch.equal(runner.generate(prompt, 5), reference.generate(prompt, 5))   # plans are reusable after reset
+    for _ in range(3):
+        runner.step()            # positions 7, then 8 and 9: past the cache
+    torch.cuda.synchronize()
+    assert int(runner.step_status.item()) == 1
 
 
 def test_generate_is_repeatable_and_checks_the_cache_length():
