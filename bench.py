@@ -94,6 +94,31 @@ def log(*parts) -> None:
     print(*parts, file=sys.stderr, flush=True)
 
 
+class nvtx_range:
+    """NVTX range around a profiled region (the reference's profiler marks each operator the same way,
+    scripts/profile_kernel.py:346-354); a no-op where torch's NVTX bindings are not usable."""
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        try:
+            import torch
+
+            torch.cuda.nvtx.range_push(self.name)
+            self.pushed = True
+        except Exception:
+            self.pushed = False
+        return self
+
+    def __exit__(self, *exc):
+        if self.pushed:
+            import torch
+
+            torch.cuda.nvtx.range_pop()
+        return False
+
+
 def algorithmic_bytes(m: int, k: int, n: int) -> int:
     return n * k // 2 + n * (k // GROUP) * 2 + m * k * 2 + m * n * 2
 
@@ -548,8 +573,9 @@ def run_single_layer(args) -> dict:
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.profiler.start()
     start.record()
-    for i in range(args.steps):
-        linear_cuda(x, pk[i % copies], sc[i % copies], GROUP)
+    with nvtx_range(f"w4a16.linear M={m} K={k} N={n}"):
+        for i in range(args.steps):
+            linear_cuda(x, pk[i % copies], sc[i % copies], GROUP)
     end.record()
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
@@ -583,7 +609,9 @@ def run_decode_step(args) -> dict:
         model = transformers.AutoModelForCausalLM.from_config(cfg, dtype=torch.float16)
     model.eval()
     replace_linear_layers(model, group_size=GROUP)
-    runner = LlamaDecodeRunner(model, max_len=16 + args.steps + 8)
+    runner = LlamaDecodeRunner(model, max_len=16 + args.steps + 8, persistent=args.persistent)
+    if args.persistent:
+        runner._enqueue_step = runner._persistent_step      # one cooperative launch per token
     prompt = torch.randint(0, 32000, (16,), generator=torch.Generator().manual_seed(0)).to(device)
     with torch.inference_mode():
         for i in range(16):
@@ -594,8 +622,9 @@ def run_decode_step(args) -> dict:
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.profiler.start()
         start.record()
-        for _ in range(args.steps):
-            runner._enqueue_step()
+        for index in range(args.steps):
+            with nvtx_range(f"w4a16.decode_step {index}"):
+                runner._enqueue_step()
         end.record()
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
@@ -959,7 +988,8 @@ def run_product(args) -> dict:
     sampler.active.set()
     launches_before = lib.w4a16_launch_count()
     torch.cuda.profiler.start()   # `ncu --profile-from-start off` captures exactly the timed region
-    ms = time_replays(torch, graph, args.steps)
+    with nvtx_range("w4a16.timed_region tinyllama_decode_linears_m1"):
+        ms = time_replays(torch, graph, args.steps)
     torch.cuda.profiler.stop()
     barrier()
     ms = max_over_ranks(ms)
@@ -1196,17 +1226,19 @@ def run_reference(args) -> dict:
     """
     if int(os.environ.get("RANK", "0")) != 0:
         return {}
-    ref_root = ROOT / "oracle" / "_ref"
-    use_ref = all((ref_root / "w4a16" / name).is_file() for name in ("__init__.py", "quantization.pyc", "reference.pyc"))
-    if use_ref:
-        sys.path.insert(0, str(ref_root))
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("_w4a16_build_ref", ROOT / "oracle" / "build_ref.py")
+    ref_recipe = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref_recipe)
+    use_ref = ref_recipe.available()
     import torch
 
     torch.set_num_threads(os.cpu_count() or 1)
     if use_ref:
-        from w4a16 import quantization as ref_quant, reference as ref_linear   # the reference's modules
+        ref_quant, ref_linear = ref_recipe.load()     # the reference's own modules, compiled
 
-        assert pathlib.Path(ref_linear.__file__).resolve().is_relative_to(ref_root.resolve())
+        assert "nibble_b200" not in sys.modules
         kind = "reference"
 
         def quantise(w):
@@ -1275,6 +1307,8 @@ def main() -> None:
     parser.add_argument("--workload", choices=["tinyllama_decode_linears_m1", "llama70b_tp", "decode_step", "decode"],
                         default="tinyllama_decode_linears_m1")
     parser.add_argument("--batch", type=int, default=1, help="M for --workload llama70b_tp")
+    parser.add_argument("--persistent", action="store_true",
+                        help="--workload decode_step: the step as one cooperative launch instead of a chain of kernels")
     parser.add_argument("--cpu-blocks", type=int, default=1,
                         help="--impl reference: decoder blocks (7 linears each) per step")
     parser.add_argument("--collective", choices=["p2p", "nccl"], default="p2p",

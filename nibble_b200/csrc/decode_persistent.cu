@@ -140,7 +140,8 @@ __device__ __forceinline__ float cta_max(float v, float* scratch) {
 // scores and softmax, FP32 accumulation of the values).  D/8 consecutive lanes share a cached position.
 // Shared memory (all inside `smem`): scores[max_len] floats, then the fixed part below.
 template <int D>
-__device__ __forceinline__ void attention_head(const AttentionOp& p, int head, unsigned char* smem, unsigned* status) {
+__device__ __forceinline__ void attention_head(const AttentionOp& p, int head, unsigned char* smem, unsigned* status,
+                                               GridSync& sync) {
     constexpr int kLanesPerPos = D / 8;
     constexpr int kPosPerPass = kThreads / kLanesPerPos;
     constexpr int half_d = D / 2;
@@ -156,7 +157,15 @@ __device__ __forceinline__ void attention_head(const AttentionOp& p, int head, u
     const int slot = tid / kLanesPerPos;
     const uint4* k_rows = reinterpret_cast<const uint4*>(p.k_cache + static_cast<size_t>(kv_head) * p.max_len * D) + sub;
     const uint4* v_rows = reinterpret_cast<const uint4*>(p.v_cache + static_cast<size_t>(kv_head) * p.max_len * D) + sub;
+    // Nothing requested here depends on the operation before this one (it produces qkv): the position only moves
+    // at the end of a step and the older cache rows were written by earlier steps.  So the first pass of K and V
+    // rows is requested before the hand-off is waited for; rows at or past the position are fetched (inside the
+    // cache) and never used.
     const long long pos = __ldcg(p.position);
+    const int early_t = min(slot, p.max_len - 1);
+    const uint4 k_early = __ldcg(k_rows + static_cast<size_t>(early_t) * kLanesPerPos);
+    const uint4 v_early = __ldcg(v_rows + static_cast<size_t>(early_t) * kLanesPerPos);
+    sync.wait_for_previous();
     if (pos < 0 || pos >= p.max_len) {
         if (tid == 0) atomicMax(status, 1u);
         return;
@@ -188,8 +197,9 @@ __device__ __forceinline__ void attention_head(const AttentionOp& p, int head, u
 
     const int length = static_cast<int>(pos) + 1;
     // The newest position comes from shared memory, not from the cache: another CTA writes it there.
-    auto row_piece = [&](const uint4* rows, const __half* newest, int t) {
+    auto row_piece = [&](const uint4* rows, const __half* newest, const uint4& early, int t) {
         if (t == length - 1) return reinterpret_cast<const uint4*>(newest)[sub];
+        if (t < kPosPerPass) return early;
         return __ldcg(rows + static_cast<size_t>(t) * kLanesPerPos);
     };
     float qf[8];
@@ -202,7 +212,7 @@ __device__ __forceinline__ void attention_head(const AttentionOp& p, int head, u
         const int t = base + slot;
         float dot = 0.0f;
         if (t < length) {
-            const uint4 piece = row_piece(k_rows, k_new, t);
+            const uint4 piece = row_piece(k_rows, k_new, k_early, t);
             const __half2* h = reinterpret_cast<const __half2*>(&piece);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -233,7 +243,7 @@ __device__ __forceinline__ void attention_head(const AttentionOp& p, int head, u
         const int t = base + slot;
         if (t < length) {
             const float w = scores[t];
-            const uint4 piece = row_piece(v_rows, v_new, t);
+            const uint4 piece = row_piece(v_rows, v_new, v_early, t);
             const __half2* h = reinterpret_cast<const __half2*>(&piece);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -311,16 +321,19 @@ decode_step_kernel(const StepParams s, const int head_dim) {
         if (kind == kOpLinear) {
             const MmaParams p = s.ops[i].linear;
             StepHooks hooks{sync};
-            linear_mma_body<1, 1, 1, kStepKW, 2, kStepStages>(p, smem, hooks);
+            linear_mma_body<1, 1, 1, kStepKW, 2, kStepStages, kFeatRowIndex>(p, smem, hooks);
         } else if (kind == kOpAttention) {
             const AttentionOp p = s.ops[i].attention;
-            sync.wait_for_previous();
             if (static_cast<int>(blockIdx.x) < p.q_heads) {
                 if (head_dim == 64) {
-                    attention_head<64>(p, blockIdx.x, smem, s.status);
+                    attention_head<64>(p, blockIdx.x, smem, s.status, sync);
                 } else {
-                    attention_head<128>(p, blockIdx.x, smem, s.status);
+                    attention_head<128>(p, blockIdx.x, smem, s.status, sync);
                 }
+            } else {
+                // A CTA without a head still waits: the counter only means "operation i - 1 is complete" while no
+                // CTA arrives at operation i before it has seen that itself.
+                sync.wait_for_previous();
             }
             sync.arrive();
         } else {

@@ -63,7 +63,17 @@ __global__ void __launch_bounds__(kThreads, min_ctas_per_sm<NT, TILES>())
 linear_mma_kernel(const MmaParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     KernelHooks hooks;
-    linear_mma_body<NT, XB, TILES, KW, U, STAGES>(p, smem, hooks);
+    linear_mma_body<NT, XB, TILES, KW, U, STAGES, 0>(p, smem, hooks);
+}
+
+// The same kernel with the tensor-parallel sender and reader paths compiled in (launches that carry a
+// w4a16_peer_target or a w4a16_peer_source).
+template <int NT, int XB, int TILES, int KW, int U, int STAGES>
+__global__ void __launch_bounds__(kThreads, min_ctas_per_sm<NT, TILES>())
+linear_mma_exchange_kernel(const MmaParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    KernelHooks hooks;
+    linear_mma_body<NT, XB, TILES, KW, U, STAGES, kFeatExchange>(p, smem, hooks);
 }
 
 
@@ -166,6 +176,7 @@ __global__ void sum_partials_kernel(const void* __restrict__ partials, __half* _
 // ------------------------------------------------------------------------------------------------
 struct Variant {
     const void* fn;
+    const void* fn_exchange;   // the build with the tensor-parallel paths; null where it is not instantiated
     int red_bytes;     // shared memory for the cross-warp reduction
     int stage_bytes;   // shared memory of one pipeline stage
     int stages;
@@ -176,7 +187,11 @@ template <int NT, int XB, int TILES, int KW, int U, int STAGES>
 Variant variant_of() {
     constexpr int RW = kWarpsPerCta / KW;
     constexpr int red = KW > 1 ? 2 * KW * TILES * NT * 4 * 32 * RW * static_cast<int>(sizeof(float)) : 0;
-    return {reinterpret_cast<const void*>(&linear_mma_kernel<NT, XB, TILES, KW, U, STAGES>), red,
+    const void* exchange = nullptr;
+    if constexpr (TILES == 1) {   // sharded layers always run one 16-row tile per warp
+        exchange = reinterpret_cast<const void*>(&linear_mma_exchange_kernel<NT, XB, TILES, KW, U, STAGES>);
+    }
+    return {reinterpret_cast<const void*>(&linear_mma_kernel<NT, XB, TILES, KW, U, STAGES>), exchange, red,
             stage_bytes<TILES, U>(), STAGES, XB};
 }
 
@@ -560,6 +575,11 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
     // Opt in to large dynamic shared memory once per device and kernel variant (the attribute belongs to
     // the function as loaded on one device), and learn its occupancy there (cached per device, variant
     // and shared-memory size).
+    const void* kernel = variant.fn;
+    if (prob.peers != nullptr || prob.source != nullptr) {
+        if (variant.fn_exchange == nullptr) return W4A16_ERR_BAD_CONFIG;
+        kernel = variant.fn_exchange;
+    }
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess) return W4A16_ERR_LAUNCH;
     static std::mutex mutex;
@@ -567,16 +587,16 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
     int blocks_per_sm = 0;
     {
         std::lock_guard<std::mutex> lock(mutex);
-        const auto key = std::make_tuple(device, variant.fn, smem);
+        const auto key = std::make_tuple(device, kernel, smem);
         const auto found = occupancy.find(key);
         if (found != occupancy.end()) {
             blocks_per_sm = found->second;
         } else {
-            if (cudaFuncSetAttribute(variant.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) !=
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) !=
                 cudaSuccess) {
                 return W4A16_ERR_LAUNCH;
             }
-            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, variant.fn, kThreads, smem) !=
+            if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, kernel, kThreads, smem) !=
                     cudaSuccess || blocks_per_sm < 1) {
                 return W4A16_ERR_LAUNCH;
             }
@@ -604,7 +624,7 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
     launch.attrs = attr;
     launch.numAttrs = programmatic ? 1 : 0;
     void* args[] = {const_cast<MmaParams*>(&params)};
-    if (cudaLaunchKernelExC(&launch, variant.fn, args) != cudaSuccess) return W4A16_ERR_LAUNCH;
+    if (cudaLaunchKernelExC(&launch, kernel, args) != cudaSuccess) return W4A16_ERR_LAUNCH;
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return W4A16_OK;
 }

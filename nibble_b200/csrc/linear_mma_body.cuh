@@ -294,7 +294,14 @@ __device__ __noinline__ void stage_tagged(const uint4* base, size_t row_units, i
 // whole weight ring has been requested and must return only when x may be read and y written;
 // `hooks.after_outputs()` runs when this CTA has written its last output.  The function may be called
 // repeatedly by a persistent kernel: it leaves no copy in flight and no state in shared memory.
-template <int NT, int XB, int TILES, int KW, int U, int STAGES, typename Hooks>
+//
+// FEATURES selects optional code at compile time, so that the plain kernel -- whose small launches are bound by
+// instruction fetch and prologue latency -- carries none of it: kFeatExchange = the tensor-parallel sender and
+// reader paths (peer_out / src_* parameters), kFeatRowIndex = the x_row_index parameter.
+constexpr int kFeatExchange = 1;
+constexpr int kFeatRowIndex = 2;
+
+template <int NT, int XB, int TILES, int KW, int U, int STAGES, int FEATURES, typename Hooks>
 __device__ __forceinline__ void linear_mma_body(const MmaParams& p, unsigned char* smem, Hooks& hooks) {
     constexpr int RW = kWarpsPerCta / KW;
     constexpr int kRowsPerTile = 16 * TILES;
@@ -439,14 +446,17 @@ __device__ __forceinline__ void linear_mma_body(const MmaParams& p, unsigned cha
     // satisfied long ago).  As a reader nothing is waited for here: the staging loop below re-reads elements
     // of x that have not arrived yet.
     const __half* x_in = p.x;
-    if (p.x_row_index != nullptr) x_in += static_cast<size_t>(__ldcg(p.x_row_index)) * static_cast<size_t>(p.x_ld);
+    constexpr bool kExchange = (FEATURES & kFeatExchange) != 0;
+    if constexpr ((FEATURES & kFeatRowIndex) != 0) {
+        if (p.x_row_index != nullptr) x_in += static_cast<size_t>(__ldcg(p.x_row_index)) * static_cast<size_t>(p.x_ld);
+    }
     unsigned src_epoch = 0, out_epoch = 0, out_tag = 0;
     size_t out_offset = 0;
-    if (p.src_epoch != nullptr) {
+    if (kExchange && p.src_epoch != nullptr) {
         src_epoch = __ldcg(p.src_epoch);
         x_in = reinterpret_cast<const __half*>(reinterpret_cast<const char*>(p.x) + (src_epoch & 1u) * p.src_stride);
     }
-    if (p.peer_out != nullptr) {
+    if (kExchange && p.peer_out != nullptr) {
         out_epoch = __ldcg(p.send_epoch) + 1u;
         out_tag = tag_of(out_epoch);
         if (warp == 1) wait_for_flags(p.consumed, p.world, out_epoch - 2u, p.wait_polls, p.peer_status, kReaderCodeBase);
@@ -470,7 +480,7 @@ __device__ __forceinline__ void linear_mma_body(const MmaParams& p, unsigned cha
                          "r"(prmt(q.y, q.w, 0x7632u))
                          : "memory");
         };
-        if (p.src_epoch != nullptr) {
+        if (kExchange && p.src_epoch != nullptr) {
             const int staged_rows = XB == 1 ? 1 : batch_here;
             const uint4* base = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned*>(x_in) +
                                                                static_cast<size_t>(m0) * p.x_ld +
@@ -577,7 +587,7 @@ __device__ __forceinline__ void linear_mma_body(const MmaParams& p, unsigned cha
         }
     }
     __syncthreads();
-    if (p.src_epoch != nullptr && tid == 0) {
+    if (kExchange && p.src_epoch != nullptr && tid == 0) {
         // the last CTA to have read its part of x gives the buffer back to the senders
         const unsigned ctas = gridDim.x * gridDim.y * gridDim.z;
         if (atomicAdd(p.staged_counter, 1u) == ctas - 1) {
@@ -727,7 +737,7 @@ __device__ __forceinline__ void linear_mma_body(const MmaParams& p, unsigned cha
     // Final destination of one output element: this rank's y, or the same position in the result
     // buffer of every rank of the group (plain stores over NVLink into peer-mapped memory).
     auto write_out = [&](int row, size_t m, float sum) {
-        if (p.peer_out == nullptr) {
+        if (!kExchange || p.peer_out == nullptr) {
             if (p.out_f32) {
                 static_cast<float*>(p.y)[m * p.N + row] = sum;
             } else {
@@ -912,7 +922,7 @@ __device__ __forceinline__ void linear_mma_body(const MmaParams& p, unsigned cha
     }
     cp_async_wait<0>();   // nothing of this thread may still be landing in shared memory at exit
 
-    if (p.peer_out != nullptr && tid == 0) {
+    if (kExchange && p.peer_out != nullptr && tid == 0) {
         // The tagged elements need no flag behind them; the last CTA only counts the publication, for this
         // rank's readers (which run after this kernel has completed) and for the next launch.
         const unsigned ctas = gridDim.x * gridDim.y * gridDim.z;

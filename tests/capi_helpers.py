@@ -10,6 +10,10 @@ from nibble_b200 import _native
 from oracle import w4a16_oracle as oracle
 
 
+_CANARY = 512            # FP16 elements either side of an output (a multiple of 8 keeps the output 16-byte aligned)
+_CANARY_VALUE = -1234.0
+
+
 def _stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
@@ -23,7 +27,12 @@ def new_workspace(m: int, n: int, k: int, splits: int = 8) -> torch.Tensor:
 def capi_linear(x, packed, scales, group_size=128, *, workspace=None, flags=0, config=None, expect=0):
     m, k = x.shape
     n = packed.shape[0]
-    y = torch.full((m, n), float("nan"), dtype=torch.float16, device=x.device)
+    # The output sits between two canary zones (this pool has no compute-sanitizer): a kernel that writes outside
+    # [M, N] disturbs them, one that skips an element leaves its NaN in place.
+    guarded = torch.full((2 * _CANARY + m * n,), float("nan"), dtype=torch.float16, device=x.device)
+    guarded[:_CANARY] = _CANARY_VALUE
+    guarded[_CANARY + m * n:] = _CANARY_VALUE
+    y = guarded[_CANARY:_CANARY + m * n].view(m, n)
     ws_ptr = ctypes.c_void_p(workspace.data_ptr()) if workspace is not None else None
     ws_bytes = workspace.numel() if workspace is not None else 0
     args = [
@@ -37,6 +46,8 @@ def capi_linear(x, packed, scales, group_size=128, *, workspace=None, flags=0, c
         cfg = _native.LinearConfig(*config)
         status = lib.w4a16_linear_f16_config(*args, ctypes.byref(cfg), _stream())
     assert status == expect, f"status {status}: {_native.status_string(status)}"
+    assert bool((guarded[:_CANARY] == _CANARY_VALUE).all()) and bool((guarded[_CANARY + m * n:] == _CANARY_VALUE).all()), \
+        "the kernel wrote outside its output"
     return y
 
 

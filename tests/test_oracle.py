@@ -192,15 +192,15 @@ def test_oracle_against_the_compiled_reference_modules(tmp_path):
     import sys
 
     root = pathlib.Path(__file__).resolve().parent.parent
-    ref = root / "oracle" / "_ref"
-    if not (ref / "w4a16" / "reference.pyc").is_file():
+    if not (root / "oracle" / "_ref" / "w4a16" / "reference.bin").is_file():
         pytest.skip("oracle/_ref is not built (no checkout of the reference on this machine)")
     out = tmp_path / "ref.npz"
     script = f"""
 import sys
-sys.path.insert(0, {str(ref)!r})
+sys.path.insert(0, {str(root / "oracle")!r})
 import numpy as np, torch
-from w4a16 import quantization as q, reference as r
+import build_ref
+q, r = build_ref.load()
 assert 'nibble_b200' not in sys.modules
 g = torch.Generator().manual_seed(42)
 w = torch.randn((96, 640), generator=g) * 0.02
