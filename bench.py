@@ -315,6 +315,9 @@ def prefill_table(torch, device) -> dict:
             log(f"  prefill {name} K={k} N={n} M={m}: {row}")
         del packed, scales, w16
         torch.cuda.empty_cache()
+    from nibble_b200 import check_device_status
+
+    check_device_status()      # no bounded wait of the tcgen05 kernel may have given up
     return out
 
 
@@ -1045,8 +1048,11 @@ def run_product(args) -> dict:
         barrier()
         fused_ms = time_replays(torch, fused_graph, args.steps) / args.steps
         fused_bytes = sum(algorithmic_bytes(1, x.shape[1], packed.shape[0]) for x, packed, _ in fused_layers)
+        fused_value = fused_bytes / (fused_ms * 1e-3) / 1e9
         fused_siblings = {"launches_per_step": len(fused_layers), "ms_per_step": round(fused_ms, 5),
-                          "value": round(fused_bytes / (fused_ms * 1e-3) / 1e9, 1), "bytes_per_step": fused_bytes}
+                          "value": round(fused_value, 1), "bytes_per_step": fused_bytes,
+                          "roofline_frac": round(fused_value / measured_peaks()[0], 4),
+                          "what": "the same token as replace_linear_layers serves it by default: q/k/v and gate/up as one launch each"}
         log(f"  q/k/v and gate/up as single launches: {fused_siblings}")
         del fused_graph, fused_layers, fused_outs
         torch.cuda.empty_cache()

@@ -258,7 +258,11 @@ int w4a16_linear_f16_input(const void* x, const void* packed, const void* scales
  *   softmax(q k^T * softmax_scale) v over positions 0..*position to out [q_heads*d].  d is 64 or
  *   128.  A position outside [0, max_len) sets *status to 1 and nothing is written.
  * flags: W4A16_FLAG_PROGRAMMATIC_LAUNCH as for the linear (each kernel waits for its predecessor before
- *   it reads or writes memory).
+ *   it reads or writes memory).  One exception, for latency: attention_decode reads *position, inv_freq and
+ *   the cache rows below the position BEFORE that wait.  A programmatic chain only orders a kernel after its
+ *   immediate predecessor, so nothing launched programmatically ahead of an attention_decode may write
+ *   `position` or the caches without a fully serialising (ordinary) launch in between -- e.g. put the kernel
+ *   that advances the position at the end of a step and start the next step with an ordinary launch.
  */
 int w4a16_add_rmsnorm_f16(const void* stream_in, const void* delta, const void* weight, void* stream_out,
                           void* normed, int64_t hidden, float eps, uint32_t flags, w4a16_stream_t stream);

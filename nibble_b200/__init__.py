@@ -1,7 +1,8 @@
 """B200-native W4A16 linear path with the reference project's Python surface."""
 from .checkpoint import (load_packed_model, load_quantized_model_checkpoint, load_quantized_weight_checkpoint,
                          save_quantized_model_checkpoint, save_quantized_weight_checkpoint)
-from .cuda import cuda_extension_available, dequantize_cuda, linear_cuda, quantize_and_pack_cuda
+from .cuda import (check_device_status, cuda_extension_available, dequantize_cuda, linear_cuda,
+                   quantize_and_pack_cuda)
 from .fusion import FusedQuantizedLinear, FusedSlice, fuse_parallel_linears
 from .integration import load_packed_state_dict, replace_linear_layers
 from .linear import Int4Linear, QuantizedLinear
@@ -28,4 +29,5 @@ __all__ = [
     "dequantize_cuda",
     "quantize_and_pack_cuda",
     "cuda_extension_available",
+    "check_device_status",
 ]

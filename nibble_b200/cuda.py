@@ -68,6 +68,26 @@ def programmatic_launch_enabled() -> bool:
     return os.environ.get("W4A16_PDL") == "1"
 
 
+def check_device_status() -> None:
+    """Raise if a bounded wait inside the prefill (tcgen05) kernel gave up since the last check.
+
+    The kernel never hangs: a barrier wait that exceeds its poll limit records a code in a device word and the
+    kernel still runs to the end of its clean-up -- with an unfinished result.  Callers of the prefill route
+    (``torch.ops.w4a16.linear`` with 65 rows or more) should call this where they synchronise anyway, e.g. after a
+    prompt has been processed.  Synchronises the device; clears the word.
+    """
+    import ctypes
+
+    _require_extension()
+    value = ctypes.c_uint32(0)
+    status = _native.core().w4a16_device_status(ctypes.byref(value))
+    if status != 0:
+        raise RuntimeError(f"w4a16_device_status failed: {_native.status_string(status)}")
+    if value.value:
+        raise RuntimeError(f"a W4A16 prefill kernel gave up waiting on a barrier (code 0x{value.value:x}); "
+                           "its output is incomplete")
+
+
 def cuda_extension_available() -> bool:
     """True when the compiled operator library loaded."""
     return _EXTENSION_LOAD_ERROR is None

@@ -311,6 +311,9 @@ class LlamaDecodeRunner:
                 self.v_cache[index, :, :count].copy_(layer.values[0, :, :count])
             self.token.copy_(out.logits[0, -1:].argmax(-1))
             self.position.fill_(count)
+        from .cuda import check_device_status
+
+        check_device_status()      # the batched forward ran the prefill kernels: none of their waits may have given up
 
     def generate(self, prompt_ids: torch.Tensor, new_tokens: int, batched_prefill: bool | None = None) -> torch.Tensor:
         """Greedy continuation of a 1-D prompt; returns the ``new_tokens`` generated ids."""
