@@ -362,6 +362,14 @@ size_t w4a16_static_scratch_bytes(void);
  * unfinished result).  Reading synchronises the device and clears the word.  No reference counterpart. */
 int w4a16_device_status(uint32_t* value);
 
+/* Checked build only (the library compiled with -DW4A16_BOUNDS_CHECK, `python nibble_b200/_build.py --bounds-check`):
+ * the streaming kernel compares every shared- and global-memory index it computes with the extent it must stay
+ * inside, skips an access that would leave it and counts it.  *count = violations since the last call, *site = the
+ * highest site code among them (1 activation staging, 2 output, 3 split-K partial, 4 weight copy, 5 scale copy);
+ * reading synchronises and clears.  The ordinary build returns W4A16_ERR_BAD_CONFIG.  No reference counterpart
+ * (the reference relies on compute-sanitizer, README.md:199-210). */
+int w4a16_bounds_check_status(uint32_t* site, uint32_t* count);
+
 /* Number of kernels this library has launched in this process (all entry points, all devices). */
 uint64_t w4a16_launch_count(void);
 

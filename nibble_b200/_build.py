@@ -24,6 +24,7 @@ CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 OBJ = PKG / "build"
 CORE_LIB = PKG / "libw4a16_b200.so"
+CHECKED_LIB = PKG / "libw4a16_b200_checked.so"
 TORCH_LIB = PKG / "_C.so"
 
 CUDA_SOURCES = ["capi.cu", "linear_mma.cu", "linear_generic.cu", "dequantize.cu", "linear_static_scratch.cu", "linear_tcgen05.cu", "quantize.cu", "decode_ops.cu", "decode_persistent.cu"]
@@ -82,6 +83,22 @@ def build_core(force: bool = False) -> pathlib.Path:
     return CORE_LIB
 
 
+def build_checked(force: bool = False) -> pathlib.Path:
+    """``libw4a16_b200_checked.so``: the core library with the streaming kernel compiled with
+    ``-DW4A16_BOUNDS_CHECK`` (every index compared with its extent; see ``w4a16_bounds_check_status``).  Only
+    ``linear_mma.cu`` is compiled again; the other objects are those of the ordinary build."""
+    build_core(force)
+    if not force and CHECKED_LIB.exists() and CHECKED_LIB.stat().st_mtime >= max(_sources_mtime(), CORE_LIB.stat().st_mtime):
+        return CHECKED_LIB
+    nvcc = _nvcc()
+    checked = OBJ / "linear_mma.cu.checked.o"
+    _run([nvcc, *NVCC_FLAGS, "-DW4A16_BOUNDS_CHECK", "-I", str(INCLUDE), "-c", str(CSRC / "linear_mma.cu"), "-o", str(checked)],
+         log=OBJ / "linear_mma.cu.checked.ptxas.log")
+    objects = [checked if name == "linear_mma.cu" else OBJ / (name + ".o") for name in CUDA_SOURCES]
+    _run([nvcc, "-shared", "-o", str(CHECKED_LIB), *map(str, objects)])
+    return CHECKED_LIB
+
+
 def build_torch_shim(force: bool = False) -> pathlib.Path:
     """Compile ``csrc/int4_linear.cpp`` against the installed torch and link it to the core library."""
     build_core(force)
@@ -117,3 +134,5 @@ def build_all(force: bool = False) -> None:
 if __name__ == "__main__":
     build_all(force="--force" in sys.argv)
     print("built", CORE_LIB, "and", TORCH_LIB)
+    if "--bounds-check" in sys.argv:
+        print("built", build_checked(force="--force" in sys.argv))

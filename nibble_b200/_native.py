@@ -13,6 +13,7 @@ import pathlib
 
 PKG = pathlib.Path(__file__).resolve().parent
 CORE_LIB = PKG / "libw4a16_b200.so"
+CHECKED_LIB = PKG / "libw4a16_b200_checked.so"     # the same library built with -DW4A16_BOUNDS_CHECK
 TORCH_LIB = PKG / "_C.so"
 
 
@@ -126,6 +127,7 @@ C_API = {
                                                ctypes.POINTER(DecodePlanInfo), _P]),
     "w4a16_decode_step_f16": (ctypes.c_int, [_P, ctypes.POINTER(DecodePlanInfo), _P]),
     "w4a16_device_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32)]),
+    "w4a16_bounds_check_status": (ctypes.c_int, [ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint32)]),
     "w4a16_launch_count": (ctypes.c_uint64, []),
     "w4a16_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "w4a16_abi_version": (ctypes.c_int, []),
@@ -149,11 +151,16 @@ FLAG_NO_TCGEN05 = 1 << 3
 
 @functools.lru_cache(maxsize=None)
 def core() -> ctypes.CDLL:
-    if not CORE_LIB.exists():
+    import os
+
+    path = CORE_LIB
+    if os.environ.get("W4A16_CHECKED_LIB") == "1":     # tests: the bounds-checking build, C ABI calls only
+        path = CHECKED_LIB
+    if not path.exists():
         raise RuntimeError(
-            f"{CORE_LIB.name} is not built; run `python nibble_b200/_build.py` (needs nvcc)"
+            f"{path.name} is not built; run `python nibble_b200/_build.py` (needs nvcc)"
         )
-    lib = ctypes.CDLL(str(CORE_LIB))
+    lib = ctypes.CDLL(str(path))
     for name, (restype, argtypes) in C_API.items():
         fn = getattr(lib, name)  # AttributeError if the symbol is not exported
         fn.restype = restype

@@ -203,6 +203,15 @@ int w4a16_sum_partials_f16(const void* partials, void* y, int64_t count, int32_t
                                       (flags & W4A16_FLAG_PROGRAMMATIC_LAUNCH) != 0, reinterpret_cast<cudaStream_t>(stream));
 }
 
+int w4a16_bounds_check_status(uint32_t* site, uint32_t* count) {
+    if (site == nullptr || count == nullptr) return W4A16_ERR_NULL_POINTER;
+    unsigned s = 0, c = 0;
+    const int status = w4a16::read_bounds_check(&s, &c);
+    *site = s;
+    *count = c;
+    return status;
+}
+
 int w4a16_device_status(uint32_t* value) {
     if (value == nullptr) return W4A16_ERR_NULL_POINTER;
     unsigned v = 0;

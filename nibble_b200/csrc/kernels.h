@@ -45,6 +45,9 @@ w4a16_linear_config choose_linear_config(int64_t M, int64_t N, int64_t K, int ma
 int launch_linear_mma(const LinearProblem& p, const w4a16_linear_config& cfg, bool programmatic,
                       bool out_f32, cudaStream_t stream);
 
+// Bounds-check word of the streaming kernel; W4A16_ERR_BAD_CONFIG in builds without -DW4A16_BOUNDS_CHECK.
+int read_bounds_check(unsigned* site, unsigned* count);
+
 // Prefill-sized batches: dequantisation fused into a tcgen05 GEMM (group == 128, aligned x / packed).
 int launch_linear_tcgen05(const LinearProblem& p, cudaStream_t stream);
 // Status word of that kernel (non-zero: a bounded barrier wait gave up); reading clears it and synchronises.

@@ -420,6 +420,25 @@ int launch_sum_partials(const void* partials, __half* y, int64_t count, int worl
                         static_cast<long long>(count), world, r);
 }
 
+// Reads and clears the bounds-check word of the streaming kernel (builds with -DW4A16_BOUNDS_CHECK only).
+int read_bounds_check(unsigned* site, unsigned* count) {
+#ifdef W4A16_BOUNDS_CHECK
+    unsigned word[2] = {0u, 0u};
+    const unsigned zero[2] = {0u, 0u};
+    if (cudaMemcpyFromSymbol(word, g_bounds_word, sizeof(word)) != cudaSuccess ||
+        cudaMemcpyToSymbol(g_bounds_word, zero, sizeof(zero)) != cudaSuccess) {
+        return W4A16_ERR_LAUNCH;
+    }
+    *site = word[0];
+    *count = word[1];
+    return W4A16_OK;
+#else
+    *site = 0u;
+    *count = 0u;
+    return W4A16_ERR_BAD_CONFIG;
+#endif
+}
+
 int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_in, bool programmatic,
                       bool out_f32, cudaStream_t stream) {
     if (prob.group != kGroup || prob.K % kGroup != 0) return W4A16_ERR_BAD_CONFIG;

@@ -15,6 +15,18 @@
 namespace w4a16 {
 namespace {
 
+// -DW4A16_BOUNDS_CHECK: every computed shared- or global-memory index of the kernel body is compared with the
+// extent it must stay inside; a violation is counted and its site recorded in a device word (read through
+// w4a16_bounds_check_status) and the access is skipped -- never a trap.  Stands in for compute-sanitizer where
+// that tool is not available; the ordinary build compiles none of it.
+#ifdef W4A16_BOUNDS_CHECK
+static __device__ unsigned g_bounds_word[2];   // [0] highest site code seen, [1] number of violations
+#define W4A16_IN_BOUNDS(cond, site) \
+    ((cond) ? true : (atomicMax(&g_bounds_word[0], static_cast<unsigned>(site)), atomicAdd(&g_bounds_word[1], 1u), false))
+#else
+#define W4A16_IN_BOUNDS(cond, site) true
+#endif
+
 constexpr int kWarpsPerCta = 8;
 constexpr int kThreads = kWarpsPerCta * 32;
 constexpr int kSmemBudget = 220 * 1024;   // dynamic shared memory a CTA may ask for
@@ -399,6 +411,12 @@ __device__ __forceinline__ void linear_mma_body(const MmaParams& p, unsigned cha
             constexpr int OFFSET = U == 2
                 ? SLOT * kStageBytes + ((j >> 2) * 2 + ((j >> 1) & 1)) * U * kItemBytes + (j & 1) * 256
                 : SLOT * kStageBytes + j * kItemBytes;
+            // source: 16 bytes inside the packed matrix; destination: inside the ring
+            if (!W4A16_IN_BOUNDS(p_src[j] + POS * kStepBytes >= p.packed &&
+                                     p_src[j] + POS * kStepBytes + 16 <= p.packed + static_cast<size_t>(p.N) * row_bytes &&
+                                     copy_dst + OFFSET + 16 <= ring + STAGES * kStageBytes, 4)) {
+                return;
+            }
             cp_async16<OFFSET, POS * kStepBytes>(copy_dst, p_src[j]);
         }
     };
@@ -419,7 +437,10 @@ __device__ __forceinline__ void linear_mma_body(const MmaParams& p, unsigned cha
             copy_at(pos_tag, std::integral_constant<int, 6>{});
             copy_at(pos_tag, std::integral_constant<int, 7>{});
             if constexpr (U == 2) {
-                if (scale_lane) cp_async4<SLOT * kStageBytes, POS * U * 2>(ring_s + lane * 4, p_scl);
+                if (scale_lane && W4A16_IN_BOUNDS(p_scl + POS * U >= p.scales &&
+                                                      p_scl + POS * U + 2 <= p.scales + static_cast<size_t>(p.N) * p.chunks, 5)) {
+                    cp_async4<SLOT * kStageBytes, POS * U * 2>(ring_s + lane * 4, p_scl);
+                }
             }
             if (--p_left == 0) {
                 p_tile += tile_stride;
@@ -475,6 +496,7 @@ __device__ __forceinline__ void linear_mma_body(const MmaParams& p, unsigned cha
         auto put = [&](const uint4& q, int j, int n) {
             const int c = j >> 4, tt = (j >> 2) & 3, i = j & 3;
             const unsigned dst = xs + (((c * 4 + i) * XB + n) * 4 + tt) * 16;
+            if (!W4A16_IN_BOUNDS(n >= 0 && n < XB && j >= 0 && dst + 16 <= xs + static_cast<unsigned>(span) * (XB * 256), 1)) return;
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "r"(prmt(q.x, q.z, 0x5410u)),
                          "r"(prmt(q.x, q.z, 0x7632u)), "r"(prmt(q.y, q.w, 0x5410u)),
                          "r"(prmt(q.y, q.w, 0x7632u))
@@ -737,6 +759,7 @@ __device__ __forceinline__ void linear_mma_body(const MmaParams& p, unsigned cha
     // Final destination of one output element: this rank's y, or the same position in the result
     // buffer of every rank of the group (plain stores over NVLink into peer-mapped memory).
     auto write_out = [&](int row, size_t m, float sum) {
+        if (!W4A16_IN_BOUNDS(row >= 0 && row < p.N && m < static_cast<size_t>(p.M), 2)) return;
         if (!kExchange || p.peer_out == nullptr) {
             if (p.out_f32) {
                 static_cast<float*>(p.y)[m * p.N + row] = sum;
@@ -764,6 +787,7 @@ __device__ __forceinline__ void linear_mma_body(const MmaParams& p, unsigned cha
         float* stage = red + parity * (KW * kAccPerLane * 32);
         auto store = [&](int row, size_t m, float sum) {
             if (split_k) {
+                if (!W4A16_IN_BOUNDS(row >= 0 && row < p.N && m < static_cast<size_t>(p.M) && split < p.k_splits, 3)) return;
                 p.partial[(static_cast<size_t>(split) * p.M + m) * p.N + row] = sum;
             } else {
                 write_out(row, m, sum);
