@@ -815,6 +815,25 @@ def sharded_block_bench(torch, dist, device, rank: int, world: int, m: int, step
                 f"first bad columns {bad.nonzero()[:8, -1].tolist()}")
             out["peer_vs_nccl_max_rel_diff"] = round(float(diff.max()) / max(scale, 1e-30), 5)
             out["peer_equals_nccl"] = not bool(bad.any())
+            if bad.any() or os.environ.get("W4A16_BENCH_CHECK_UNSHARDED") == "1":
+                # which of the two is off?  Rebuild the unsharded layers from every rank's shards and run the chain here.
+                def all_ranks(t, dim):
+                    parts = [torch.empty_like(t) for _ in range(world)]
+                    dist.all_gather(parts, t.contiguous())
+                    return torch.cat(parts, dim).contiguous()
+
+                with torch.inference_mode():
+                    x = x0
+                    for qkv, o, gate_up, down in shards:
+                        t = linear_cuda(x, all_ranks(qkv[0], 0), all_ranks(qkv[1], 0), GROUP)
+                        t = linear_cuda(t[:, :8192].contiguous(), all_ranks(o[0], 0), all_ranks(o[1], 0), GROUP)
+                        t = linear_cuda(t, all_ranks(gate_up[0], 0), all_ranks(gate_up[1], 0), GROUP)
+                        x = linear_cuda(t[:, :28672].contiguous(), all_ranks(down[0], 1), all_ranks(down[1], 1), GROUP)
+                truth = x.float()
+                out["peer_vs_unsharded_max_rel_diff"] = round(float((a - truth).abs().max()) / max(scale, 1e-30), 5)
+                out["nccl_vs_unsharded_max_rel_diff"] = round(float((b - truth).abs().max()) / max(scale, 1e-30), 5)
+                log(f"  [rank {rank}] against the unsharded chain: peer {out['peer_vs_unsharded_max_rel_diff']}, "
+                    f"nccl {out['nccl_vs_unsharded_max_rel_diff']}")
 
         if "paired" in modes:
             blocks = []

@@ -79,7 +79,10 @@ typedef struct w4a16_linear_config {
  * Otherwise a generic kernel that accepts any even group_size and any alignment.
  * `workspace` may be NULL (then K is never split across CTAs); if given it must be 16-byte aligned,
  * hold at least w4a16_linear_workspace_bytes(M, N, K) bytes, be zero-filled before its first use
- * and not be shared by calls that may run concurrently.  The library leaves it ready for re-use.
+ * and not be shared by calls that may run concurrently.  The library leaves it ready for re-use, by calls
+ * of any shape: the arrival counters live in a fixed 256 KB prefix that partial sums never touch (problems
+ * with more than 65536 pairs of 16-row tile x 8-row batch block use a longer prefix; re-zero a workspace that
+ * such a problem shares with others).
  * M == 0 or N == 0 returns W4A16_OK without launching.
  */
 int w4a16_linear_f16(const void* x, const void* packed, const void* scales, void* y,

@@ -268,10 +268,19 @@ size_t x_slice_bytes(int rows, int chunks) { return static_cast<size_t>(rows) * 
 
 }  // namespace
 
+// The arrival counters occupy a prefix of the workspace whose size does not depend on the problem (as long as
+// the problem has at most kCounterSlots row-tile x batch-block pairs): one workspace may then serve calls of
+// different shapes one after the other, because the FP32 partial sums of one call can never land where another
+// call keeps its counters (they used to, when the prefix was sized per problem: leftover partials of an N = 2048
+// call sat in the counter slots of tiles 128.. of a following N = 2560 call, whose last arriver was then never
+// recognised and whose outputs were never written).
+constexpr int64_t kCounterSlots = 65536;
+
 size_t linear_counter_bytes(int64_t M, int64_t N) {
     const int64_t row_blocks = (N + 15) / 16;
     const int64_t batch_blocks = (M + 7) / 8;
-    const size_t bytes = static_cast<size_t>(row_blocks * batch_blocks) * sizeof(unsigned);
+    const int64_t slots = std::max<int64_t>(row_blocks * batch_blocks, kCounterSlots);
+    const size_t bytes = static_cast<size_t>(slots) * sizeof(unsigned);
     return (bytes + 255) & ~static_cast<size_t>(255);
 }
 

@@ -85,7 +85,9 @@ int w4a16_linear_f16_static_scratch(const void* x, const void* packed, const voi
     // but the array is shared and outlives calls, so they are cleared here every time rather than
     // trusted.  (The partial sums need no clearing: every element read is written first.)
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    if (cudaMemsetAsync(scratch, 0, w4a16::linear_counter_bytes(M, N), s) != cudaSuccess) return W4A16_ERR_LAUNCH;
+    // (Only the counters this problem uses; they sit at the head of the fixed counter prefix.)
+    const size_t used_counters = static_cast<size_t>((N + 15) / 16) * static_cast<size_t>((M + 7) / 8) * sizeof(unsigned);
+    if (cudaMemsetAsync(scratch, 0, used_counters, s) != cudaSuccess) return W4A16_ERR_LAUNCH;
     return w4a16_linear_f16(x, packed, scales, y, M, N, K, group_size, scratch, needed, flags, stream);
 }
 

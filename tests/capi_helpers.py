@@ -20,7 +20,7 @@ def _stream() -> ctypes.c_void_p:
 
 def new_workspace(m: int, n: int, k: int, splits: int = 8) -> torch.Tensor:
     """Zero-filled scratch large enough for `splits` K-splits (counters + FP32 partials)."""
-    counters = (((n + 15) // 16) * ((m + 7) // 8) * 4 + 255) // 256 * 256
+    counters = (max(((n + 15) // 16) * ((m + 7) // 8), 65536) * 4 + 255) // 256 * 256      # fixed 256 KB prefix
     return torch.zeros(counters + splits * m * n * 4 + 256, dtype=torch.uint8, device="cuda")
 
 

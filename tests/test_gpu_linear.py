@@ -144,6 +144,31 @@ def test_split_k_workspace_is_reusable_and_deterministic():
     check_against_oracle(capi_linear(x, packed, scales), x, packed, scales)
 
 
+def test_one_workspace_serves_calls_of_different_shapes():
+    """Split-K calls of different N share one workspace back to back (as the torch operator's per-stream workspace
+    does): the partial sums of one call must never end up where the next call keeps its arrival counters.  N = 2048
+    followed by N = 2560 at K = 8192 used to leave tiles 128.. of the second call unwritten."""
+    lib = _native.core()
+    ws = torch.zeros(8 << 20, dtype=torch.uint8, device="cuda")
+    torch.manual_seed(3)
+    x = torch.randn((1, 8192), device="cuda").half()
+    cases = []
+    for n in (2048, 2560, 1024, 4096, 2560, 256, 2048):
+        packed = torch.randint(0, 256, (n, 4096), dtype=torch.uint8, device="cuda")
+        scales = (torch.rand((n, 64), device="cuda") * 0.002 + 0.001).half()
+        assert lib.w4a16_linear_workspace_bytes(1, n, 8192) > 0 or n >= 4096, "these shapes split K"
+        cases.append((packed, scales, capi_linear(x, packed, scales, workspace=ws)))     # no synchronisation in between
+    torch.cuda.synchronize()
+    for packed, scales, y in cases:
+        assert not torch.isnan(y).any()
+        rows = np.unique(np.concatenate([np.arange(0, packed.shape[0], 37), np.arange(packed.shape[0] - 40, packed.shape[0])]))
+        check_against_oracle(y, x, packed, scales, rows=rows)
+    assert int(ws[: 256 * 1024].sum()) == 0, "arrival counters must be back at zero"
+    # the operator's own per-stream workspace, same sequence
+    for packed, scales, y in cases:
+        assert torch.equal(linear_cuda(x, packed, scales, 128), y)
+
+
 def test_programmatic_launch_flag_gives_identical_results():
     x, packed, scales = _random_case(1, 2048, 5632, seed=4, std=0.02)
     plain = capi_linear(x, packed, scales)
