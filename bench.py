@@ -815,8 +815,9 @@ def sharded_block_bench(torch, dist, device, rank: int, world: int, m: int, step
                 f"first bad columns {bad.nonzero()[:8, -1].tolist()}")
             out["peer_vs_nccl_max_rel_diff"] = round(float(diff.max()) / max(scale, 1e-30), 5)
             out["peer_equals_nccl"] = not bool(bad.any())
-            if bad.any() or os.environ.get("W4A16_BENCH_CHECK_UNSHARDED") == "1":
-                # which of the two is off?  Rebuild the unsharded layers from every rank's shards and run the chain here.
+            if bad.any() or os.environ.get("W4A16_BENCH_CHECK_UNSHARDED", "1") == "1":
+                # Parity gate of the sharded record: rebuild the unsharded layers from every rank's shards, run the same
+                # chain on this GPU alone and compare both exchanges with it.
                 def all_ranks(t, dim):
                     parts = [torch.empty_like(t) for _ in range(world)]
                     dist.all_gather(parts, t.contiguous())
