@@ -139,3 +139,39 @@ def test_column_and_row_parallel_over_nccl(tmp_path):
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
     assert sorted(name for name in os.listdir(tmp_path) if name.startswith("ok")) == ["ok0", "ok1"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_one_process_drives_two_devices():
+    """A model split over two GPUs by one process: the shared-memory opt-in and the occupancy of every kernel variant
+    are per device, so the second device must work as the first does (streaming kernel, prefill kernel, decode kernels,
+    the allocation-free entry point)."""
+    import ctypes
+
+    from capi_helpers import check_against_oracle
+    from nibble_b200 import _native, linear_cuda, quantize_and_pack_weights
+
+    g = torch.Generator().manual_seed(0)
+    packed, scales = quantize_and_pack_weights(torch.randn((320, 4096), generator=g) * 0.02, 128)
+    for m in (1, 8, 96):
+        x = torch.randn((m, 4096), generator=g).half()
+        outs = []
+        for device in ("cuda:1", "cuda:0", "cuda:1"):
+            with torch.cuda.device(device):
+                y = linear_cuda(x.to(device), packed.to(device), scales.to(device), 128)
+                torch.cuda.synchronize()
+            check_against_oracle(y, x, packed, scales, fp16_weights=m >= 65)
+            outs.append(y.cpu())
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    lib = _native.core()
+    for device in ("cuda:1", "cuda:0"):
+        with torch.cuda.device(device):
+            x = torch.randn((1, 8192), generator=g).half().to(device)
+            p = torch.randint(0, 256, (1024, 4096), dtype=torch.uint8, device=device)
+            s = (torch.rand((1024, 64), device=device) * 0.002 + 0.001).half()
+            y = torch.full((1, 1024), float("nan"), dtype=torch.float16, device=device)
+            status = lib.w4a16_linear_f16_static_scratch(x.data_ptr(), p.data_ptr(), s.data_ptr(), y.data_ptr(), 1, 1024, 8192, 128, 0,
+                                                         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+            torch.cuda.synchronize()
+            assert status == 0 and not torch.isnan(y).any()
+            assert torch.equal(y, linear_cuda(x, p, s, 128))
