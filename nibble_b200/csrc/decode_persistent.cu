@@ -108,6 +108,7 @@ struct GridSync {
 // the previous operation is waited for, and its end is announced to the next one.
 struct StepHooks {
     GridSync& sync;
+    __device__ __forceinline__ void at_start() {}
     __device__ __forceinline__ void before_activations() { sync.wait_for_previous(); }
     __device__ __forceinline__ void after_outputs() { sync.arrive(); }
 };

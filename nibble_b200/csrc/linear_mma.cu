@@ -51,10 +51,10 @@ namespace {
 
 // Hooks of the stand-alone kernel: programmatic dependent launch on the way in, nothing on the way out.
 struct KernelHooks {
-    __device__ __forceinline__ void before_activations() {
-        pdl_release_downstream();
-        pdl_wait_for_upstream();
-    }
+    // The successor is released with the very first instruction: its CTAs only take SM resources this grid does not
+    // use, and the earlier they are resident the more of their prologue and weight prefetch hides under this grid.
+    __device__ __forceinline__ void at_start() { pdl_release_downstream(); }
+    __device__ __forceinline__ void before_activations() { pdl_wait_for_upstream(); }
     __device__ __forceinline__ void after_outputs() {}
 };
 

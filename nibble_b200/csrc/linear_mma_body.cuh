@@ -333,6 +333,7 @@ __device__ __forceinline__ void linear_mma_body(const MmaParams& p, unsigned cha
     const unsigned ring = smem_addr(smem + kFlagBytes + sizeof(float) * kRedFloats * RW);
     const unsigned xs = ring + STAGES * kStageBytes;
 
+    hooks.at_start();
     const int tid = threadIdx.x;
     const int lane = tid & 31;
     const int warp = tid >> 5;
