@@ -317,7 +317,7 @@ w4a16_linear_config choose_linear_config(int64_t M, int64_t N, int64_t K, int ma
     // every k_warps x k_splits combination; Llama-70B gate/up and down projections).
     struct Tuned { int64_t n, k; int k_warps, k_splits; };
     static const Tuned tuned[] = {
-        {28672, 8192, 4, 1},   // 1792 row tiles: four warps per tile balance the last wave
+        {28672, 8192, 8, 1},   // 1792 row tiles: eight warps per tile halve the quarter-full last wave
         {8192, 28672, 1, 4},   // long K: split across CTAs so the activation slice stays small
     };
     int tuned_splits = 0;
@@ -470,15 +470,21 @@ int launch_linear_mma(const LinearProblem& prob, const w4a16_linear_config& cfg_
     const int chunks_per_split = (per_split + cfg.unroll - 1) / cfg.unroll * cfg.unroll;
     if ((splits - 1) * chunks_per_split >= chunks) return W4A16_ERR_BAD_CONFIG;   // an empty split
 
-    // Ring depth: four slots when two CTAs still fit on an SM with them, else three.
+    // Ring depth: four slots when two CTAs still fit on an SM with them; else three if that is what lets two CTAs fit;
+    // and when the activation slice is so large that only one CTA fits either way, four again (as many bytes in flight
+    // as the budget allows, and the step loop is unrolled over 4 positions instead of 6: with eight warps per SM the
+    // longer loop showed up as instruction-fetch stalls, `no_instruction` 1.26 per issue at M = 8 on 8192-wide layers).
     Variant variant;
     if (cfg.stages == 0) {
         cfg.stages = cfg.unroll == 1 ? 3 : 4;
         if (cfg.unroll == 2) {
             if (!pick_variant(nt, prob.M == 1, cfg, &variant)) return W4A16_ERR_BAD_CONFIG;
-            const size_t with_four =
-                kFlagBytes + variant.red_bytes + x_slice_bytes(x_rows, chunks_per_split) + 4u * variant.stage_bytes;
-            if (with_four > static_cast<size_t>(kSmemPerSm / 2 - 1024)) cfg.stages = 3;
+            const size_t fixed = kFlagBytes + variant.red_bytes + x_slice_bytes(x_rows, chunks_per_split);
+            const size_t half_sm = static_cast<size_t>(kSmemPerSm / 2 - 1024);
+            const bool two_with_four = fixed + 4u * variant.stage_bytes <= half_sm;
+            const bool two_with_three = fixed + 3u * variant.stage_bytes <= half_sm;
+            const bool four_fit = fixed + 4u * variant.stage_bytes <= static_cast<size_t>(kSmemBudget);
+            if (!two_with_four && (two_with_three || !four_fit)) cfg.stages = 3;
         }
     }
     if (!pick_variant(nt, prob.M == 1, cfg, &variant)) return W4A16_ERR_BAD_CONFIG;

@@ -119,7 +119,10 @@ def test_every_launch_shape(m, row_tiles, k_warps, k_splits, unroll, stages):
     stage_bytes = 256 * 2 * row_tiles * unroll * 16 + (8 * 16 * row_tiles * 4 if unroll == 2 else 0)
     red_bytes = 0 if k_warps == 1 else 2 * 8 * row_tiles * nt * 4 * 32 * 4
     fixed = 128 + x_rows * per_split * 256 + red_bytes
-    depth = stages or (3 if unroll == 1 or fixed + 4 * stage_bytes > 113 * 1024 else 4)
+    half_sm, budget = 113 * 1024, 220 * 1024
+    two_with_four, two_with_three = fixed + 4 * stage_bytes <= half_sm, fixed + 3 * stage_bytes <= half_sm
+    automatic = 3 if unroll == 1 or (not two_with_four and (two_with_three or fixed + 4 * stage_bytes > budget)) else 4
+    depth = stages or automatic
     fits = fixed + depth * stage_bytes <= 220 * 1024
     y = capi_linear(x, packed, scales, workspace=ws, config=(row_tiles, k_warps, k_splits, unroll, stages),
                     expect=(0 if fits else -5) if valid else -6)
