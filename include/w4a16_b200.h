@@ -54,7 +54,9 @@ enum {
      * results are added across devices before the single rounding to FP16. */
     W4A16_FLAG_OUTPUT_F32 = 1u << 2,
     /* Keep batches of 65 rows and more on the mma.sync kernel instead of the tcgen05 GEMM (A/B, tests). */
-    W4A16_FLAG_NO_TCGEN05 = 1u << 3
+    W4A16_FLAG_NO_TCGEN05 = 1u << 3,
+    /* Route to the tcgen05 GEMM whatever the batch size, when the fast path applies and y is FP16 (A/B, tests). */
+    W4A16_FLAG_FORCE_TCGEN05 = 1u << 4
 };
 
 /* Explicit launch shape of the fused tensor-core kernel; zero fields mean "choose for me". */
@@ -72,8 +74,9 @@ typedef struct w4a16_linear_config {
  * Replaces the reference's int4_linear_cuda (csrc/int4_linear_kernel.cu:641-802) and the kernels
  * it dispatches to (decode_multirow :325-404, small_batch :542-617, naive :20-69).
  *
- * Fast path when group_size == 128 and x, packed are 16-byte aligned: M <= 64 runs the mma.sync
- * streaming kernel, larger M a tcgen05 GEMM whose producer warps dequantise into the operand tiles
+ * Fast path when group_size == 128 and x, packed are 16-byte aligned: M <= 16 runs the mma.sync
+ * streaming kernel, M >= 65 (and 17..64 on layers of N >= 4096 where a cost model built from measurements
+ * favours it) a tcgen05 GEMM whose producer warps dequantise into the operand tiles
  * (no FP16 weight matrix in memory; weights enter the product as half(code * scale), the arithmetic of
  * the reference's dequantise-then-matmul prefill route, w4a16/linear.py:132-152).
  * Otherwise a generic kernel that accepts any even group_size and any alignment.

@@ -147,6 +147,7 @@ FLAG_PROGRAMMATIC_LAUNCH = 1 << 0
 FLAG_FORCE_GENERIC = 1 << 1
 FLAG_OUTPUT_F32 = 1 << 2
 FLAG_NO_TCGEN05 = 1 << 3
+FLAG_FORCE_TCGEN05 = 1 << 4
 
 
 @functools.lru_cache(maxsize=None)

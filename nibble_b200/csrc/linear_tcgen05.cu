@@ -13,16 +13,24 @@
 // columns, BN a multiple of 16 up to 256 chosen per call), so one pass of dequantisation feeds up to
 // 256 batch rows.
 //
-// Persistent CTAs, one per SM, each walking a strided list of output tiles; 14 warps with fixed roles:
-//   warp 0      one lane issues the TMA loads of every stage: the x tile and the packed codes of the
-//               weight tile (two tensor maps built per call on the host)
+// Persistent CTAs, one per SM, each walking a strided list of output tiles; 23 warps with fixed roles:
+//   warp 0      one lane issues the TMA loads of the x tiles, one per operand stage
+//   warp 22     one lane issues the TMA loads of the packed codes into a ring of its own (two tensor
+//               maps built per call on the host)
 //   warp 1      allocates TMEM; one lane issues the MMAs and the commits that recycle pipeline stages
 //   warps 2-5   epilogue: tcgen05.ld the accumulator of the finished tile, round to FP16, store
-//   warps 6-13  dequantisers: two threads per weight row, 32 codes each per 64-wide K block, read from
-//               the stage's packed tile -> unpack, scale, re-pair to memory order, four 16-byte stores
-//               at their swizzled places in the stage's FP16 operand tile
+//   warps 6-21  dequantisers, four groups of four warps; a group takes every fourth 64-wide K block and a
+//               thread of it one weight row: 64 codes read from the packed tile -> unpack, scale, re-pair
+//               to memory order, eight 16-byte stores at their swizzled places in the stage's FP16 tile
 // The accumulator is double buffered (2 x 256 TMEM columns), so the epilogue of one tile runs under
 // the main loop of the next.
+//
+// Two rings.  The codes are the only operand that comes from HBM, 4 KB per K block, and their slot is
+// free again as soon as the dequantisers hold it in registers: eight slots keep eight K blocks of codes
+// in flight whatever the tensor cores are doing.  An operand stage (the FP16 weight tile the
+// dequantisers write plus the x tile) is held until its MMAs have finished; its x tile comes out of L2.
+// The x tile is sized for the call's batch tile, so small batches get more operand stages (up to eight)
+// out of the same shared memory.
 //
 // Every wait on an mbarrier is bounded; a wait that gives up sets a device status word and the CTA
 // still runs to its TMEM deallocation, so a logic error ends in a reported failure, not a hung GPU.
@@ -42,16 +50,23 @@ namespace {
 
 constexpr int kBM = 128;          // output channels per tile (MMA M)
 constexpr int kMaxBN = 256;       // batch rows per tile at most (MMA N)
-constexpr int kBK = 64;           // K per pipeline stage: one 128-byte swizzle row of FP16
-constexpr int kStagesTc = 4;
-constexpr int kATileBytes = kBM * kBK * 2;        // 16 KB
-constexpr int kBTileBytes = kMaxBN * kBK * 2;     // 32 KB
-constexpr int kPackedTileBytes = kBM * kBK / 2;   // 4 KB: the codes of one weight tile as they lie in HBM
-constexpr int kStageBytes = kATileBytes + kBTileBytes + kPackedTileBytes;
-constexpr int kDequantThreads = 256;
+constexpr int kBK = 64;           // K of one operand sub-tile: one 128-byte swizzle row of FP16
+// A pipeline stage holds SUB such sub-tiles (a template parameter of the kernel): two -- one 128-wide scale
+// group per stage -- when the batch tile leaves room for three stages of that size, else one.
+constexpr int kMaxStagesTc = 8;                   // operand stages at most (fewer when the x tile is large)
+constexpr int kCodeCopyK = 256;                   // K of one copy of codes: 128 bytes of every row
+constexpr int kCodeSlots = 2;                     // ring of such copies
+constexpr int kASubTileBytes = kBM * kBK * 2;     // 16 KB
+constexpr int kPackedTileBytes = kBM * kCodeCopyK / 2;   // 16 KB: whole 128-byte lines of 128 weight rows
+constexpr int kDequantGroups = 4;                 // groups of dequantisers at most, taking the stages in turn
+constexpr int kDequantGroupWarps = kBM / 32;      // one thread per weight row
+constexpr int kDequantThreads = kDequantGroups * kBM;
 constexpr int kEpilogueThreads = 128;
 constexpr int kFirstDequantWarp = 6;
-constexpr int kThreadsTc = (kFirstDequantWarp + kDequantThreads / 32) * 32;   // 448
+constexpr int kCodesWarp = kFirstDequantWarp + kDequantThreads / 32;          // 22
+constexpr int kThreadsTc = (kCodesWarp + 1) * 32;                             // 736
+constexpr int kBarrierBytes = 512;
+constexpr int kSmemLimitTc = 227 * 1024;
 constexpr int kTmemColumns = 2 * kMaxBN;
 constexpr int kGroupM = 4;        // batch tiles walked together before moving along N
 constexpr unsigned kSpinLimit = 1u << 20;
@@ -120,6 +135,22 @@ struct TcParams {
     int M, N, K;
     int bn;            // batch rows per tile (multiple of 16)
     int m_tiles, n_tiles, total_tiles;
+    int stages;        // operand stages in use, 2..kMaxStagesTc
+    int dequant_groups;   // groups of dequantisers in use: a divisor of `stages`, see the kernel
+};
+
+// A position in a ring of `size` slots together with the parity of the mbarrier phase it is in.
+struct RingCursor {
+    int slot = 0;
+    unsigned phase = 0;
+    bool first_round = true;
+    __device__ __forceinline__ void advance(int size) {
+        if (++slot == size) {
+            slot = 0;
+            phase ^= 1u;
+            first_round = false;
+        }
+    }
 };
 
 // Tiles are numbered so that kGroupM batch tiles sharing one slab of weights are adjacent: CTAs
@@ -134,33 +165,48 @@ __device__ __forceinline__ void tile_coords(int tile, const TcParams& p, int& m_
     m_tile = first + (local - n_tile * gm);
 }
 
+template <int SUB>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_map,
                       const __grid_constant__ CUtensorMap w_map) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // 1024-byte aligned tiles (the swizzle pattern is a function of address bits 4-9)
     const unsigned base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    auto a_tile = [&](int s) { return base + s * kStageBytes; };
-    auto b_tile = [&](int s) { return base + s * kStageBytes + kATileBytes; };
-    auto packed_tile = [&](int s) { return base + s * kStageBytes + kATileBytes + kBTileBytes; };
-    const unsigned bars = base + kStagesTc * kStageBytes;
-    auto full_bar = [&](int s) { return bars + s * 8; };                       // operands of the stage are ready
-    auto empty_bar = [&](int s) { return bars + (kStagesTc + s) * 8; };        // the MMAs are done with the stage
-    auto codes_bar = [&](int s) { return bars + (2 * kStagesTc + s) * 8; };    // the packed codes have landed
-    auto acc_full_bar = [&](int b) { return bars + (3 * kStagesTc + b) * 8; };
-    auto acc_empty_bar = [&](int b) { return bars + (3 * kStagesTc + 2 + b) * 8; };
-    const unsigned tmem_slot = bars + (3 * kStagesTc + 4) * 8;
+    const unsigned x_sub_tile_bytes = static_cast<unsigned>(p.bn) * (kBK * 2);   // a multiple of 2 KB
+    constexpr int kStageK = SUB * kBK;
+    constexpr int kATileBytes = SUB * kASubTileBytes;
+    constexpr int kCodeBlocks = kCodeCopyK / kStageK;                      // stages served by one copy of codes
+    const unsigned x_tile_bytes = SUB * x_sub_tile_bytes;
+    const unsigned stage_bytes = kATileBytes + x_tile_bytes;
+    auto a_tile = [&](int s) { return base + s * stage_bytes; };
+    auto b_tile = [&](int s) { return base + s * stage_bytes + kATileBytes; };
+    const unsigned codes_ring = base + p.stages * stage_bytes;
+    auto packed_tile = [&](int c) { return codes_ring + c * kPackedTileBytes; };
+    const unsigned bars = codes_ring + kCodeSlots * kPackedTileBytes;
+    auto full_bar = [&](int s) { return bars + s * 8; };                          // operands of the stage are ready
+    auto empty_bar = [&](int s) { return bars + (kMaxStagesTc + s) * 8; };        // the MMAs are done with the stage
+    auto codes_bar = [&](int c) { return bars + (2 * kMaxStagesTc + c) * 8; };    // the packed codes have landed
+    auto codes_free_bar = [&](int c) { return bars + (2 * kMaxStagesTc + kCodeSlots + c) * 8; };   // ... and are in registers
+    constexpr int kRingBars = 2 * kMaxStagesTc + 2 * kCodeSlots;
+    auto acc_full_bar = [&](int b) { return bars + (kRingBars + b) * 8; };
+    auto acc_empty_bar = [&](int b) { return bars + (kRingBars + 2 + b) * 8; };
+    const unsigned tmem_slot = bars + (kRingBars + 4) * 8;
+    static_assert((kRingBars + 4) * 8 + 4 <= kBarrierBytes, "barrier block too small");
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const int k_blocks = p.K / kBK;
+    const int k_blocks = p.K / kStageK;                                   // pipeline stages per tile
+    const int code_chunks = (k_blocks + kCodeBlocks - 1) / kCodeBlocks;   // copies of codes per tile
 
     if (tid == 0) {
-        for (int s = 0; s < kStagesTc; ++s) {
-            mbar_init(full_bar(s), kDequantThreads / 32 + 1);   // one lane per dequantiser warp + the TMA issuer
+        for (int s = 0; s < kMaxStagesTc; ++s) {
+            mbar_init(full_bar(s), kDequantGroupWarps + 1);   // one lane per warp of a dequantiser group + the TMA issuer
             mbar_init(empty_bar(s), 1);                    // one tcgen05.commit
-            mbar_init(codes_bar(s), 1);                    // the TMA issuer
+        }
+        for (int c = 0; c < kCodeSlots; ++c) {
+            mbar_init(codes_bar(c), 1);                    // the TMA issuer
+            mbar_init(codes_free_bar(c), p.dequant_groups * kDequantGroupWarps);   // one lane per working dequantiser warp
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full_bar(b), 1);
@@ -182,33 +228,47 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
 
     bool healthy = true;
     if (warp == 0) {
-        // ---------------- TMA: the packed weight tile and the x tile of every stage ----------------------
+        // ---------------- TMA: the x tile of every operand stage ----------------------------------------
         if (lane == 0) {
-            unsigned it = 0;
-            const unsigned tile_bytes = static_cast<unsigned>(p.bn) * (kBK * 2);
+            RingCursor at;
             for (int tile = blockIdx.x; tile < p.total_tiles && healthy; tile += gridDim.x) {
                 int m_tile, n_tile;
                 tile_coords(tile, p, m_tile, n_tile);
                 const int m0 = m_tile * p.bn;
-                const int n0 = n_tile * kBM;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int stage = it % kStagesTc;
-                    const unsigned round = it / kStagesTc;
-                    if (round > 0) healthy = mbar_wait(empty_bar(stage), (round - 1) & 1, 0x10u + stage);
+                for (int kb = 0; kb < k_blocks; ++kb, at.advance(p.stages)) {
+                    if (!at.first_round) healthy = mbar_wait(empty_bar(at.slot), at.phase ^ 1u, 0x10u + at.slot);
                     if (!healthy) break;
-                    mbar_arrive_expect_tx(codes_bar(stage), kPackedTileBytes);
+                    mbar_arrive_expect_tx(full_bar(at.slot), x_tile_bytes);
+#pragma unroll
+                    for (int sub = 0; sub < SUB; ++sub) {
+                        asm volatile(
+                            "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                            "[%0], [%1, {%2, %3}], [%4];"
+                            ::"r"(b_tile(at.slot) + sub * x_sub_tile_bytes), "l"(reinterpret_cast<uint64_t>(&x_map)),
+                            "r"(kb * kStageK + sub * kBK), "r"(m0), "r"(full_bar(at.slot))
+                            : "memory");
+                    }
+                }
+            }
+        }
+    } else if (warp == kCodesWarp) {
+        // ---------------- TMA: the packed codes, as far ahead as their ring allows ------------------------
+        if (lane == 0) {
+            RingCursor at;
+            for (int tile = blockIdx.x; tile < p.total_tiles && healthy; tile += gridDim.x) {
+                int m_tile, n_tile;
+                tile_coords(tile, p, m_tile, n_tile);
+                const int n0 = n_tile * kBM;
+                for (int chunk = 0; chunk < code_chunks; ++chunk, at.advance(kCodeSlots)) {
+                    if (!at.first_round) healthy = mbar_wait(codes_free_bar(at.slot), at.phase ^ 1u, 0x60u + at.slot);
+                    if (!healthy) break;
+                    mbar_arrive_expect_tx(codes_bar(at.slot), kPackedTileBytes);
+                    // (a box that reaches past K/2 bytes is filled with zero codes and still counts in full)
                     asm volatile(
                         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
                         "[%0], [%1, {%2, %3}], [%4];"
-                        ::"r"(packed_tile(stage)), "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(kb * (kBK / 2)), "r"(n0),
-                        "r"(codes_bar(stage))
-                        : "memory");
-                    mbar_arrive_expect_tx(full_bar(stage), tile_bytes);
-                    asm volatile(
-                        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-                        "[%0], [%1, {%2, %3}], [%4];"
-                        ::"r"(b_tile(stage)), "l"(reinterpret_cast<uint64_t>(&x_map)), "r"(kb * kBK), "r"(m0),
-                        "r"(full_bar(stage))
+                        ::"r"(packed_tile(at.slot)), "l"(reinterpret_cast<uint64_t>(&w_map)), "r"(chunk * (kCodeCopyK / 2)),
+                        "r"(n0), "r"(codes_bar(at.slot))
                         : "memory");
                 }
             }
@@ -219,25 +279,28 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
             const uint32_t instr_desc = (1u << 4)                                        // FP32 accumulate
                                         | (static_cast<uint32_t>(p.bn >> 3) << 17)       // N
                                         | (static_cast<uint32_t>(kBM >> 4) << 24);       // M; FP16, K-major A and B
-            unsigned it = 0, done_tiles = 0;
+            unsigned done_tiles = 0;
+            RingCursor at;
             for (int tile = blockIdx.x; tile < p.total_tiles && healthy; tile += gridDim.x, ++done_tiles) {
                 const unsigned buf = done_tiles & 1, use = done_tiles >> 1;
                 if (use > 0) healthy = mbar_wait(acc_empty_bar(buf), (use - 1) & 1, 0x40u + buf);
                 if (!healthy) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned acc = tmem_base + buf * kMaxBN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int stage = it % kStagesTc;
-                    const unsigned round = it / kStagesTc;
-                    healthy = mbar_wait(full_bar(stage), round & 1, 0x20u + stage);
+                for (int kb = 0; kb < k_blocks; ++kb, at.advance(p.stages)) {
+                    const int stage = at.slot;
+                    healthy = mbar_wait(full_bar(stage), at.phase, 0x20u + stage);
                     if (!healthy) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint64_t a_desc = operand_desc(a_tile(stage));
-                    const uint64_t b_desc = operand_desc(b_tile(stage));
 #pragma unroll
-                    for (int j = 0; j < kBK / 16; ++j) {
-                        // 16 k = 32 bytes further along the swizzled row: +2 in 16-byte address units
-                        umma_f16(acc, a_desc + 2 * j, b_desc + 2 * j, instr_desc, (kb > 0 || j > 0) ? 1u : 0u);
+                    for (int sub = 0; sub < SUB; ++sub) {
+                        const uint64_t a_desc = operand_desc(a_tile(stage) + sub * kASubTileBytes);
+                        const uint64_t b_desc = operand_desc(b_tile(stage) + sub * x_sub_tile_bytes);
+#pragma unroll
+                        for (int j = 0; j < kBK / 16; ++j) {
+                            // 16 k = 32 bytes further along the swizzled row: +2 in 16-byte address units
+                            umma_f16(acc, a_desc + 2 * j, b_desc + 2 * j, instr_desc, (kb > 0 || sub > 0 || j > 0) ? 1u : 0u);
+                        }
                     }
                     umma_commit(empty_bar(stage));   // arrives when these MMAs have finished reading the stage
                 }
@@ -285,59 +348,102 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
             mbar_arrive(acc_empty_bar(buf));         // this thread's part of the accumulator is in registers or stored
         }
     } else {
-        // ---------------- dequantisers: threads 2r, 2r+1 share weight row r of the tile ------------------
+        // ---------------- dequantisers: group g takes K blocks g, g+4, ...; thread r of it weight row r ----
+        // What a thread spends per K block is mostly waiting -- about 0.1 us per mbarrier wait, whatever the
+        // barrier's state, and the latency of its own chain of instructions -- not issue slots.  So the four
+        // groups work on four K blocks at once, each warp on its own (one lane waits and signals for it);
+        // the MMA issuer takes the stages in order whichever group fills them.
         const int t = tid - kFirstDequantWarp * 32;
-        const int r = t >> 1;
-        const int half_k = t & 1;                                        // which 32 of the 64 k of a block
+        const int group = t / kBM;
+        const int r = t % kBM;
         const unsigned row_offset = (r >> 3) * 1024 + (r & 7) * 128;     // row r inside a swizzled tile
         const unsigned swz = r & 7;
-        const unsigned codes_offset = r * (kBK / 2) + half_k * 16;       // this thread's 16 bytes of a packed tile
+        // The codes of a stage are 2*SUB of the eight 16-byte units of the row's 128 bytes in a copy, each at the
+        // place the copy's 128-byte swizzle gave it.
+        //
+        // A parity wait is exact only for a waiter that is within one phase of the barrier.  So every working
+        // group waits for every copy of codes and gives every slot back, also the copies none of its stages lie
+        // in (the slot's barrier counts one arrival per working warp); and the host picks the number of working
+        // groups as a divisor of the number of operand stages, so that a group meets each of its stages in
+        // every round of the ring.
+        constexpr int kUnits = 2 * SUB;
+        const int active = p.dequant_groups;
         const int groups = p.K / kGroup;
-        unsigned it = 0;
-        for (int tile = blockIdx.x; tile < p.total_tiles && healthy; tile += gridDim.x) {
+        unsigned blocks_before = 0;                                      // stages of the tiles already done
+        unsigned chunks_before = 0;                                      // ... and copies of codes
+        for (int tile = blockIdx.x; tile < p.total_tiles && healthy && group < active;
+             tile += gridDim.x, blocks_before += k_blocks, chunks_before += code_chunks) {
             int m_tile, n_tile;
             tile_coords(tile, p, m_tile, n_tile);
             // rows past N hold zero codes (the tensor map fills them); their scale is the last row's
             const int w_row = min(n_tile * kBM + r, p.N - 1);
             const __half* s_ptr = p.scales + static_cast<size_t>(w_row) * groups;
-            // a scale serves two K blocks and is requested two blocks before its first use
-            uint32_t s16 = ldg_nc_u16(s_ptr);
-            uint32_t next_s16 = ldg_nc_u16(s_ptr + min(1, groups - 1));
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                const int stage = it % kStagesTc;
-                const unsigned round = it / kStagesTc;
-                if ((kb & 1) == 0 && kb > 0) {
-                    s16 = next_s16;
-                    next_s16 = ldg_nc_u16(s_ptr + min((kb >> 1) + 1, groups - 1));
-                }
-                // the codes landing also means the MMAs that last read this stage's operand tile are done:
-                // the issuer waited for that before it asked for the codes
-                healthy = mbar_wait(codes_bar(stage), round & 1, 0x50u + stage);
+            // scales (one per 128 K) are requested three of this group's stages before their use
+            auto scale_of = [&](int kb) {
+                return static_cast<uint32_t>(ldg_nc_u16(s_ptr + min(kb * kStageK / kGroup, groups - 1)));
+            };
+            uint32_t s_now = scale_of(group);
+            uint32_t s_next = scale_of(group + active);
+            uint32_t s_after = scale_of(group + 2 * active);
+            int kb = group;                                              // this group's next stage of the tile
+            for (int c = 0; c < code_chunks && healthy; ++c) {
+                const unsigned chunk = chunks_before + static_cast<unsigned>(c);
+                const int code_slot = static_cast<int>(chunk % kCodeSlots);
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait(codes_bar(code_slot), (chunk / kCodeSlots) & 1u, 0x50u + code_slot) ? 1 : 0;
+                healthy = __shfl_sync(0xffffffffu, ok, 0) != 0;      // also orders the lanes' reads after lane 0's wait
                 if (!healthy) break;
-                uint32_t words[4];
-                asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(words[0]), "=r"(words[1]), "=r"(words[2]), "=r"(words[3])
-                             : "r"(packed_tile(stage) + codes_offset));
-                const unsigned a_row = a_tile(stage) + row_offset;
-                const uint32_t scale2 = s16 | (s16 << 16);
+                const int chunk_end = min(k_blocks, (c + 1) * kCodeBlocks);
+                for (; kb < chunk_end; kb += active) {
+                    const unsigned first_unit = static_cast<unsigned>(kb % kCodeBlocks) * kUnits;
+                    const unsigned it = blocks_before + static_cast<unsigned>(kb);      // position in the operand ring
+                    const int stage = static_cast<int>(it % static_cast<unsigned>(p.stages));
+                    const unsigned round = it / static_cast<unsigned>(p.stages);
+                    const uint32_t s16 = s_now;
+                    s_now = s_next;
+                    s_next = s_after;
+                    s_after = scale_of(kb + 3 * active);
+                    uint4 words[kUnits];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t h[4];
-                    unpack8(words[c], h);                       // (c0,c4) (c1,c5) (c2,c6) (c3,c7)
+                    for (int u = 0; u < kUnits; ++u) {
+                        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(words[u].x), "=r"(words[u].y), "=r"(words[u].z), "=r"(words[u].w)
+                                     : "r"(packed_tile(code_slot) + row_offset + (((first_unit + u) ^ swz) << 4))
+                                     : "memory");
+                    }
+                    // the operand tile may be overwritten once the MMAs that last read this stage are done
+                    if (round > 0) {
+                        if (lane == 0) ok = mbar_wait(empty_bar(stage), (round - 1u) & 1u, 0x70u + stage) ? 1 : 0;
+                        healthy = __shfl_sync(0xffffffffu, ok, 0) != 0;
+                        if (!healthy) break;
+                    }
+                    const uint32_t scale2 = s16 | (s16 << 16);
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) h[j] = hmul2_u32(h[j], scale2);
-                    const uint32_t v0 = prmt(h[0], h[1], 0x5410u);   // (c0,c1)
-                    const uint32_t v1 = prmt(h[2], h[3], 0x5410u);   // (c2,c3)
-                    const uint32_t v2 = prmt(h[0], h[1], 0x7632u);   // (c4,c5)
-                    const uint32_t v3 = prmt(h[2], h[3], 0x7632u);   // (c6,c7)
-                    const unsigned piece = static_cast<unsigned>(half_k * 4 + c) ^ swz;
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_row + (piece << 4)), "r"(v0), "r"(v1),
-                                 "r"(v2), "r"(v3)
-                                 : "memory");
+                    for (int w = 0; w < 4 * kUnits; ++w) {
+                        const uint4 quad = words[w >> 2];
+                        const uint32_t word = (w & 3) == 0 ? quad.x : (w & 3) == 1 ? quad.y : (w & 3) == 2 ? quad.z : quad.w;
+                        uint32_t h[4];
+                        unpack8(word, h);                           // (c0,c4) (c1,c5) (c2,c6) (c3,c7)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) h[j] = hmul2_u32(h[j], scale2);
+                        const uint32_t v0 = prmt(h[0], h[1], 0x5410u);   // (c0,c1)
+                        const uint32_t v1 = prmt(h[2], h[3], 0x5410u);   // (c2,c3)
+                        const uint32_t v2 = prmt(h[0], h[1], 0x7632u);   // (c4,c5)
+                        const uint32_t v3 = prmt(h[2], h[3], 0x7632u);   // (c6,c7)
+                        // word w holds k = 8w .. 8w+7 of the stage: sub-tile w / 8, 16-byte piece w % 8 of the row
+                        const unsigned piece = static_cast<unsigned>(w & 7) ^ swz;
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a_tile(stage) + (w >> 3) * kASubTileBytes +
+                                                                                       row_offset + (piece << 4)),
+                                     "r"(v0), "r"(v1), "r"(v2), "r"(v3)
+                                     : "memory");
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
+                    __syncwarp();                                    // every lane has written its row and fenced
+                    if (lane == 0) mbar_arrive(full_bar(stage));     // (release: the stores come first)
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy writes -> tensor-core reads
-                __syncwarp();                                                  // every lane has written and fenced
-                if (lane == 0) mbar_arrive(full_bar(stage));
+                if (!healthy) break;
+                __syncwarp();                                        // every lane holds the codes it wanted of this copy
+                if (lane == 0) mbar_arrive(codes_free_bar(code_slot));
             }
         }
     }
@@ -399,9 +505,9 @@ int launch_linear_tcgen05(const LinearProblem& prob, cudaStream_t stream) {
     CUtensorMap w_map;
     const cuuint64_t w_dims[2] = {static_cast<cuuint64_t>(prob.K / 2), static_cast<cuuint64_t>(prob.N)};
     const cuuint64_t w_strides[1] = {static_cast<cuuint64_t>(prob.K / 2)};
-    const cuuint32_t w_box[2] = {kBK / 2, kBM};
+    const cuuint32_t w_box[2] = {kCodeCopyK / 2, kBM};   // 128 bytes of 128 rows, swizzled like an operand tile
     if (encode(&w_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(prob.packed), w_dims, w_strides, w_box,
-               element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+               element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
         return W4A16_ERR_LAUNCH;
     }
@@ -409,24 +515,40 @@ int launch_linear_tcgen05(const LinearProblem& prob, cudaStream_t stream) {
     TcParams params{prob.packed, prob.scales, static_cast<__half*>(prob.y),
                     static_cast<int>(prob.M), static_cast<int>(prob.N), static_cast<int>(prob.K),
                     static_cast<int>(bn), static_cast<int>(m_tiles), static_cast<int>(n_tiles),
-                    static_cast<int>(m_tiles * n_tiles)};
-    const size_t smem = kStagesTc * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers, TMEM slot */;
+                    static_cast<int>(m_tiles * n_tiles), 0};
+    // as many operand stages as fit beside the code ring: 4 with a 256-row batch tile, 8 up to 80 rows
+    const size_t fixed = static_cast<size_t>(kCodeSlots) * kPackedTileBytes + 1024 /* alignment slack */ + kBarrierBytes;
+    const size_t sub_bytes = kASubTileBytes + static_cast<size_t>(bn) * (kBK * 2);      // A and x sub-tile
+    // 128-wide stages (half as many waits, fences and commits for the thread that issues the MMAs, which sets the
+    // pace of small batch tiles) when three of them fit: batch tiles of up to 128 rows
+    const int sub_tiles = (kSmemLimitTc - fixed) / (2 * sub_bytes) >= 3 ? 2 : 1;
+    const size_t stage_bytes = sub_tiles * sub_bytes;
+    // stages in use / dequantiser groups in use (a divisor of the former): 2/2, 3/3, 4/4, 6/3, 8/4
+    const size_t fit = (kSmemLimitTc - fixed) / stage_bytes;
+    params.stages = fit >= 8 ? 8 : fit >= 6 ? 6 : fit >= 4 ? 4 : fit >= 3 ? 3 : 2;
+    params.dequant_groups = params.stages == 8 ? 4 : params.stages == 6 ? 3 : params.stages;
+    if (fit < 2) return W4A16_ERR_TOO_LARGE;
+    const size_t smem = params.stages * stage_bytes + fixed;
+    const void* kernel = sub_tiles == 2 ? reinterpret_cast<const void*>(linear_tcgen05_kernel<2>)
+                                        : reinterpret_cast<const void*>(linear_tcgen05_kernel<1>);
     // the shared-memory attribute and the SM count are kept per device
     static int sm_count[64] = {};
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return W4A16_ERR_LAUNCH;
     if (sm_count[device] == 0) {
         int sms = 0;
-        if (cudaFuncSetAttribute(linear_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem)) != cudaSuccess ||
+        if (cudaFuncSetAttribute(linear_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSmemLimitTc) != cudaSuccess ||
+            cudaFuncSetAttribute(linear_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSmemLimitTc) != cudaSuccess ||
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
             return W4A16_ERR_LAUNCH;
         }
         sm_count[device] = sms;
     }
     const int grid = static_cast<int>(std::min<int64_t>(params.total_tiles, sm_count[device]));
-    linear_tcgen05_kernel<<<grid, kThreadsTc, smem, stream>>>(params, x_map, w_map);
-    if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
+    void* args[] = {&params, &x_map, &w_map};
+    if (cudaLaunchKernel(kernel, dim3(grid), dim3(kThreadsTc), args, smem, stream) != cudaSuccess) return W4A16_ERR_LAUNCH;
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     return W4A16_OK;
 }

@@ -77,7 +77,12 @@ def test_workspace_size_query():
     assert lib.w4a16_linear_workspace_bytes_flags(512, 8192, 8192, _native.FLAG_NO_TCGEN05) > 0
     assert lib.w4a16_linear_workspace_bytes_flags(512, 8192, 8192, _native.FLAG_OUTPUT_F32) > 0
     assert lib.w4a16_linear_workspace_bytes_flags(1, 1024, 8192, _native.FLAG_FORCE_GENERIC) == 0
-    assert lib.w4a16_linear_workspace_bytes_flags(32, 8192, 8192, 0) == lib.w4a16_linear_workspace_bytes(32, 8192, 8192) > 4 << 20
+    assert lib.w4a16_linear_workspace_bytes_flags(16, 8192, 8192, 0) == lib.w4a16_linear_workspace_bytes(16, 8192, 8192) > 1 << 20
+    # 17..64 rows: large layers go to the GEMM as well (no scratch), small ones stay on the streaming kernel
+    assert lib.w4a16_linear_workspace_bytes(32, 8192, 8192) == 0
+    assert lib.w4a16_linear_workspace_bytes_flags(32, 8192, 8192, _native.FLAG_NO_TCGEN05) > 4 << 20
+    assert lib.w4a16_linear_workspace_bytes(32, 1024, 8192) > 0
+    assert lib.w4a16_linear_workspace_bytes_flags(8, 1024, 8192, _native.FLAG_FORCE_TCGEN05) == 0
 
 
 def test_missing_library_is_an_error(monkeypatch, tmp_path):

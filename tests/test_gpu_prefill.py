@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from capi_helpers import capi_linear, check_against_oracle
+from capi_helpers import capi_linear, check_against_oracle, new_workspace
 from nibble_b200 import _native, quantize_and_pack_weights
 from oracle import w4a16_oracle as oracle
 
@@ -67,6 +67,65 @@ def test_tcgen05_many_tiles(m, k, n):
     torch.testing.assert_close(y.float(), ref, rtol=2e-3, atol=2e-3)
     rows = np.random.default_rng(m).choice(n, size=64, replace=False)
     check_against_oracle(y, x, packed, scales, rows=np.sort(rows), fp16_weights=True)
+
+
+@pytest.mark.parametrize(("m", "k", "n"), [
+    (17, 384, 128),       # three 128-wide stages: the last copy of codes of a tile is half used
+    (40, 640, 256),       # five stages, two tiles
+    (64, 1152, 384),      # nine stages
+    (128, 896, 200),      # seven stages, 128-row batch tile (three operand stages, three working groups)
+    (130, 640, 128),      # 64-wide stages (batch tile above 128 rows), ten of them: a half-used last copy
+    (256, 384, 256),      # six 64-wide stages
+    (200, 128, 128),      # two 64-wide stages: half a copy in all
+])
+def test_forced_gemm_on_odd_stage_counts(m, k, n):
+    """Stage counts that do not fill the last copy of codes, for both stage widths, through the flag that
+    sends any batch to the GEMM."""
+    _device_status()
+    x, packed, scales = _case(m, k, n, seed=m * 7 + k)
+    y = capi_linear(x, packed, scales, flags=_native.FLAG_FORCE_TCGEN05)
+    torch.cuda.synchronize()
+    assert _device_status() == 0
+    check_against_oracle(y, x, packed, scales, fp16_weights=True)
+    again = capi_linear(x, packed, scales, flags=_native.FLAG_FORCE_TCGEN05)
+    assert torch.equal(y, again)
+
+
+@pytest.mark.parametrize("m", [17, 32, 33, 64])
+def test_medium_batches_on_a_large_layer_take_the_gemm(m):
+    """A layer of K = 8192, N = 4096 is cheaper on the GEMM than on the streaming kernel from 33 rows on (batches
+    are padded to 32 or 64 rows there): the default route then gives what the forced GEMM gives, bit for bit, and
+    needs no scratch; below, what the streaming kernel gives.  The two agree within the tolerance."""
+    k, n = 8192, 4096
+    lib = _native.core()
+    takes_gemm = lib.w4a16_linear_workspace_bytes(m, n, k) == 0
+    assert takes_gemm == (m > 32), "the cost model moved: 32 rows stay on the streaming kernel here, 33 do not"
+    _device_status()
+    x, packed, scales = _case(m, k, n, seed=m)
+    ws = new_workspace(m, n, k)
+    y = capi_linear(x, packed, scales, workspace=ws)
+    forced = capi_linear(x, packed, scales, flags=_native.FLAG_FORCE_TCGEN05)
+    streaming = capi_linear(x, packed, scales, workspace=ws, flags=_native.FLAG_NO_TCGEN05)
+    torch.cuda.synchronize()
+    assert _device_status() == 0
+    assert torch.equal(y, forced if takes_gemm else streaming)
+    torch.testing.assert_close(forced, streaming, rtol=1e-2, atol=1e-2)
+    rows = np.sort(np.random.default_rng(m).choice(n, size=32, replace=False))
+    check_against_oracle(forced, x, packed, scales, rows=rows, fp16_weights=True)
+
+
+def test_batch_too_large_for_the_streaming_kernel_without_scratch_takes_the_gemm():
+    """32 rows of K = 28672 do not fit one CTA's shared memory unsplit; without a workspace the call used to fall
+    to the generic kernel (milliseconds) and now runs the GEMM."""
+    m, k, n = 32, 28672, 256
+    _device_status()
+    x, packed, scales = _case(m, k, n, seed=5)
+    y = capi_linear(x, packed, scales, workspace=None)
+    forced = capi_linear(x, packed, scales, flags=_native.FLAG_FORCE_TCGEN05)
+    torch.cuda.synchronize()
+    assert _device_status() == 0
+    assert torch.equal(y, forced)
+    check_against_oracle(y, x, packed, scales, fp16_weights=True)
 
 
 def test_all_nibble_values_and_repeatability(golden):
