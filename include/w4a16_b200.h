@@ -80,6 +80,9 @@ typedef struct w4a16_linear_config {
  * (no FP16 weight matrix in memory; weights enter the product as half(code * scale), the arithmetic of
  * the reference's dequantise-then-matmul prefill route, w4a16/linear.py:132-152).
  * Otherwise a generic kernel that accepts any even group_size and any alignment.
+ * The GEMM shares the K of an output tile between up to four CTAs when a layer has too few 128-row tiles for the
+ * SMs (FP32 partial sums in the workspace, added in order and rounded once by a second small kernel); without
+ * enough workspace it runs unsplit.
  * `workspace` may be NULL (then K is never split across CTAs); if given it must be 16-byte aligned,
  * hold at least w4a16_linear_workspace_bytes(M, N, K) bytes, be zero-filled before its first use
  * and not be shared by calls that may run concurrently.  The library leaves it ready for re-use, by calls

@@ -30,6 +30,36 @@ bool fast_path_applies(const void* x, const void* packed, int64_t K, int64_t gro
 
 }  // namespace
 
+namespace {
+
+// Whether a fast-path call with FP16 output goes to the tcgen05 GEMM rather than the streaming kernel.
+// From 65 rows on always.  Between 17 and 64 rows the streaming kernel still wins on small layers, but its cost
+// grows with the batch and with K (every CTA stages batch x K activations, K is split ever further and the partial
+// sums travel through memory) while the GEMM's does not.  Both sides of the comparison are fits to measurements
+// on B200: the GEMM takes about 0.6 us per 128-wide K step of a round of 148 weight tiles whatever the batch; the
+// streaming kernel about 5 us plus (8 + 1.5 * K/1024) us per 1e9 multiply-adds of the batch padded to 32 or 64
+// rows.  Layers of fewer than 32 weight tiles leave most SMs of the GEMM idle and stay on the streaming kernel.
+bool routes_to_tcgen05(int64_t M, int64_t N, int64_t K, uint32_t flags) {
+    if (flags & (W4A16_FLAG_OUTPUT_F32 | W4A16_FLAG_NO_TCGEN05 | W4A16_FLAG_FORCE_GENERIC)) return false;
+    if ((flags & W4A16_FLAG_FORCE_TCGEN05) || M >= w4a16::kTcgen05MinRows) return true;
+    if (M <= 16 || N < 4096) return false;
+    const double padded = M <= 32 ? 32.0 : 64.0;
+    const double giga_macs = padded * static_cast<double>(K) * static_cast<double>(N) * 1e-9;
+    const double streaming_us = 5.0 + giga_macs * (8.0 + 1.5 * static_cast<double>(K) / 1024.0);
+    const int64_t rounds = ((N + 127) / 128 + 147) / 148;
+    // (a layer of few tiles shares the K of a tile between CTAs and pays a second small launch for the sum)
+    const int splits = w4a16::tcgen05_k_splits(M, N, K, nullptr);
+    const double gemm_us = 3.5 + 0.6 * static_cast<double>(rounds) * static_cast<double>(K) / (128.0 * splits) +
+                           (splits > 1 ? 3.0 : 0.0);
+    return gemm_us < streaming_us;
+}
+
+}  // namespace
+
+bool w4a16::linear_routes_to_tcgen05(int64_t M, int64_t N, int64_t K, uint32_t flags) {
+    return routes_to_tcgen05(M, N, K, flags);
+}
+
 extern "C" {
 
 int w4a16_abi_version(void) { return 2; }
@@ -51,35 +81,11 @@ const char* w4a16_status_string(int status) {
     }
 }
 
-namespace {
-
-// Whether a fast-path call with FP16 output goes to the tcgen05 GEMM rather than the streaming kernel.
-// From 65 rows on always.  Between 17 and 64 rows the streaming kernel still wins on small layers, but its cost
-// grows with the batch and with K (every CTA stages batch x K activations, K is split ever further and the partial
-// sums travel through memory) while the GEMM's does not.  Both sides of the comparison are fits to measurements
-// on B200: the GEMM takes about 0.6 us per 128-wide K step of a round of 148 weight tiles whatever the batch; the
-// streaming kernel about 5 us plus (8 + 1.5 * K/1024) us per 1e9 multiply-adds of the batch padded to 32 or 64
-// rows.  Layers of fewer than 32 weight tiles leave most SMs of the GEMM idle and stay on the streaming kernel.
-bool routes_to_tcgen05(int64_t M, int64_t N, int64_t K, uint32_t flags) {
-    if (flags & (W4A16_FLAG_OUTPUT_F32 | W4A16_FLAG_NO_TCGEN05 | W4A16_FLAG_FORCE_GENERIC)) return false;
-    if ((flags & W4A16_FLAG_FORCE_TCGEN05) || M >= w4a16::kTcgen05MinRows) return true;
-    if (M <= 16 || N < 4096) return false;
-    const double padded = M <= 32 ? 32.0 : 64.0;
-    const double giga_macs = padded * static_cast<double>(K) * static_cast<double>(N) * 1e-9;
-    const double streaming_us = 5.0 + giga_macs * (8.0 + 1.5 * static_cast<double>(K) / 1024.0);
-    const int64_t rounds = ((N + 127) / 128 + 147) / 148;
-    const double gemm_us = 3.5 + 0.6 * static_cast<double>(rounds) * static_cast<double>(K) / 128.0;
-    return gemm_us < streaming_us;
-}
-
-}  // namespace
-
 size_t w4a16_linear_workspace_bytes_flags(int64_t M, int64_t N, int64_t K, uint32_t flags) {
     if (M <= 0 || N <= 0 || K <= 0 || K % w4a16::kGroupFast != 0) return 0;
-    // Calls that w4a16_linear_f16 routes away from the streaming kernel never split K: the generic kernel and the
-    // tcgen05 GEMM use no scratch.
+    // The generic kernel uses no scratch; the tcgen05 GEMM wants some only for layers with few tiles.
     if (flags & W4A16_FLAG_FORCE_GENERIC) return 0;
-    if (routes_to_tcgen05(M, N, K, flags)) return 0;
+    if (routes_to_tcgen05(M, N, K, flags)) return w4a16::tcgen05_workspace_bytes(M, N, K);
     const w4a16_linear_config c = w4a16::choose_linear_config(M, N, K, w4a16::kMaxKSplits);
     return w4a16::linear_workspace_bytes_for(M, N, c.k_splits);
 }

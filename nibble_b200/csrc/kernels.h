@@ -52,7 +52,13 @@ int read_bounds_check(unsigned* site, unsigned* count);
 int launch_linear_tcgen05(const LinearProblem& p, cudaStream_t stream);
 // Status word of that kernel (non-zero: a bounded barrier wait gave up); reading clears it and synchronises.
 int read_tcgen05_status(unsigned* value);
-constexpr int kTcgen05MinRows = 65;     // smaller batches stay on the mma.sync kernel
+constexpr int kTcgen05MinRows = 65;     // from here on every fast-path call with FP16 output takes the GEMM
+// Scratch the GEMM wants (FP32 partial sums of K ranges, for layers with few tiles); it runs unsplit without.
+size_t tcgen05_workspace_bytes(int64_t M, int64_t N, int64_t K);
+// K ranges per output tile the GEMM uses when it has that scratch (1: none); *split_k receives the width of a range.
+int tcgen05_k_splits(int64_t M, int64_t N, int64_t K, int64_t* split_k);
+// Whether w4a16_linear_f16 sends a fast-path call with these sizes and flags to the GEMM (capi.cu).
+bool linear_routes_to_tcgen05(int64_t M, int64_t N, int64_t K, uint32_t flags);
 
 // Any even group size, any alignment, any M.
 int launch_linear_generic(const LinearProblem& p, bool out_f32, cudaStream_t stream);

@@ -74,7 +74,13 @@ int w4a16_linear_f16_static_scratch(const void* x, const void* packed, const voi
     // The split the library wants for this problem, on the route this call will take, decides how
     // much scratch is needed (none when the batch goes to the tcgen05 GEMM).
     const size_t needed = w4a16_linear_workspace_bytes_flags(M, N, K, flags);
-    if (needed > kStaticScratchBytes) return W4A16_ERR_TOO_LARGE;
+    if (needed > kStaticScratchBytes) {
+        // the GEMM runs without scratch too (K not split across CTAs); the streaming kernel's split is not optional
+        if (w4a16::linear_routes_to_tcgen05(M, N, K, flags)) {
+            return w4a16_linear_f16(x, packed, scales, y, M, N, K, group_size, nullptr, 0, flags, stream);
+        }
+        return W4A16_ERR_TOO_LARGE;
+    }
     if (needed == 0) {
         return w4a16_linear_f16(x, packed, scales, y, M, N, K, group_size, nullptr, 0, flags, stream);
     }

@@ -137,6 +137,9 @@ struct TcParams {
     int m_tiles, n_tiles, total_tiles;
     int stages;        // operand stages in use, 2..kMaxStagesTc
     int dequant_groups;   // groups of dequantisers in use: a divisor of `stages`, see the kernel
+    int k_splits;         // CTAs that share one output tile, each taking a range of K (1: none)
+    int split_k;          // K of one such range: a multiple of 256 (whole copies of codes)
+    float* partial;       // [k_splits, M, N] FP32 sums of the ranges when k_splits > 1, else null
 };
 
 // A position in a ring of `size` slots together with the parity of the mbarrier phase it is in.
@@ -196,8 +199,25 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const int k_blocks = p.K / kStageK;                                   // pipeline stages per tile
-    const int code_chunks = (k_blocks + kCodeBlocks - 1) / kCodeBlocks;   // copies of codes per tile
+    // A work item is one output tile, or one K range of it when the layer has too few tiles for the SMs: item
+    // t is range t % k_splits of tile t / k_splits, so the CTAs that share a tile run side by side.
+    struct Item {
+        int m_tile, n_tile, split;
+        int first_block;   // first pipeline stage of the range, in stages of the whole K
+        int k_blocks;      // stages in the range
+        int code_chunks;   // copies of codes in the range
+    };
+    auto item_of = [&](int item) {
+        Item it;
+        it.split = item % p.k_splits;
+        tile_coords(item / p.k_splits, p, it.m_tile, it.n_tile);
+        const int k_begin = it.split * p.split_k;
+        const int k_end = min(p.K, k_begin + p.split_k);
+        it.first_block = k_begin / kStageK;
+        it.k_blocks = (k_end - k_begin) / kStageK;
+        it.code_chunks = (it.k_blocks + kCodeBlocks - 1) / kCodeBlocks;
+        return it;
+    };
 
     if (tid == 0) {
         for (int s = 0; s < kMaxStagesTc; ++s) {
@@ -232,10 +252,9 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
         if (lane == 0) {
             RingCursor at;
             for (int tile = blockIdx.x; tile < p.total_tiles && healthy; tile += gridDim.x) {
-                int m_tile, n_tile;
-                tile_coords(tile, p, m_tile, n_tile);
-                const int m0 = m_tile * p.bn;
-                for (int kb = 0; kb < k_blocks; ++kb, at.advance(p.stages)) {
+                const Item item = item_of(tile);
+                const int m0 = item.m_tile * p.bn;
+                for (int kb = item.first_block; kb < item.first_block + item.k_blocks; ++kb, at.advance(p.stages)) {
                     if (!at.first_round) healthy = mbar_wait(empty_bar(at.slot), at.phase ^ 1u, 0x10u + at.slot);
                     if (!healthy) break;
                     mbar_arrive_expect_tx(full_bar(at.slot), x_tile_bytes);
@@ -256,10 +275,10 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
         if (lane == 0) {
             RingCursor at;
             for (int tile = blockIdx.x; tile < p.total_tiles && healthy; tile += gridDim.x) {
-                int m_tile, n_tile;
-                tile_coords(tile, p, m_tile, n_tile);
-                const int n0 = n_tile * kBM;
-                for (int chunk = 0; chunk < code_chunks; ++chunk, at.advance(kCodeSlots)) {
+                const Item item = item_of(tile);
+                const int n0 = item.n_tile * kBM;
+                const int first_chunk = item.first_block / kCodeBlocks;      // ranges start at whole copies
+                for (int chunk = first_chunk; chunk < first_chunk + item.code_chunks; ++chunk, at.advance(kCodeSlots)) {
                     if (!at.first_round) healthy = mbar_wait(codes_free_bar(at.slot), at.phase ^ 1u, 0x60u + at.slot);
                     if (!healthy) break;
                     mbar_arrive_expect_tx(codes_bar(at.slot), kPackedTileBytes);
@@ -287,6 +306,7 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
                 if (!healthy) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned acc = tmem_base + buf * kMaxBN;
+                const int k_blocks = item_of(tile).k_blocks;
                 for (int kb = 0; kb < k_blocks; ++kb, at.advance(p.stages)) {
                     const int stage = at.slot;
                     healthy = mbar_wait(full_bar(stage), at.phase, 0x20u + stage);
@@ -313,16 +333,18 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
         const int quarter = warp & 3;
         unsigned done_tiles = 0;
         for (int tile = blockIdx.x; tile < p.total_tiles && healthy; tile += gridDim.x, ++done_tiles) {
-            int m_tile, n_tile;
-            tile_coords(tile, p, m_tile, n_tile);
-            const int m0 = m_tile * p.bn;
-            const int n = n_tile * kBM + quarter * 32 + lane;
+            const Item item = item_of(tile);
+            const int m0 = item.m_tile * p.bn;
+            const int n = item.n_tile * kBM + quarter * 32 + lane;
             const unsigned buf = done_tiles & 1, use = done_tiles >> 1;
             healthy = mbar_wait(acc_full_bar(buf), use & 1, 0x30u + buf);
             if (!healthy) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const unsigned taddr = tmem_base + (static_cast<unsigned>(quarter * 32) << 16) + buf * kMaxBN;
             __half* out = p.y + static_cast<size_t>(m0) * p.N + n;
+            // a K range leaves its unrounded sums; a small kernel adds the ranges in order and rounds once
+            float* out_partial = p.partial == nullptr ? nullptr
+                : p.partial + (static_cast<size_t>(item.split) * p.M + m0) * static_cast<size_t>(p.N) + n;
             for (int col = 0; col < p.bn; col += 16) {
                 uint32_t v[16];
                 asm volatile(
@@ -340,7 +362,13 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
                 if (n < p.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        if (m0 + col + j < p.M) out[static_cast<size_t>(col + j) * p.N] = __float2half_rn(__uint_as_float(v[j]));
+                        if (m0 + col + j < p.M) {
+                            if (out_partial != nullptr) {
+                                out_partial[static_cast<size_t>(col + j) * p.N] = __uint_as_float(v[j]);
+                            } else {
+                                out[static_cast<size_t>(col + j) * p.N] = __float2half_rn(__uint_as_float(v[j]));
+                            }
+                        }
                     }
                 }
             }
@@ -371,16 +399,18 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
         const int groups = p.K / kGroup;
         unsigned blocks_before = 0;                                      // stages of the tiles already done
         unsigned chunks_before = 0;                                      // ... and copies of codes
+        int k_blocks = 0, code_chunks = 0;
         for (int tile = blockIdx.x; tile < p.total_tiles && healthy && group < active;
              tile += gridDim.x, blocks_before += k_blocks, chunks_before += code_chunks) {
-            int m_tile, n_tile;
-            tile_coords(tile, p, m_tile, n_tile);
+            const Item item = item_of(tile);
+            k_blocks = item.k_blocks;
+            code_chunks = item.code_chunks;
             // rows past N hold zero codes (the tensor map fills them); their scale is the last row's
-            const int w_row = min(n_tile * kBM + r, p.N - 1);
+            const int w_row = min(item.n_tile * kBM + r, p.N - 1);
             const __half* s_ptr = p.scales + static_cast<size_t>(w_row) * groups;
             // scales (one per 128 K) are requested three of this group's stages before their use
             auto scale_of = [&](int kb) {
-                return static_cast<uint32_t>(ldg_nc_u16(s_ptr + min(kb * kStageK / kGroup, groups - 1)));
+                return static_cast<uint32_t>(ldg_nc_u16(s_ptr + min((item.first_block + kb) * kStageK / kGroup, groups - 1)));
             };
             uint32_t s_now = scale_of(group);
             uint32_t s_next = scale_of(group + active);
@@ -476,6 +506,25 @@ EncodeTiledFn tensor_map_encoder() {
 
 }  // namespace
 
+// K ranges per output tile that the GEMM wants for a problem: more than one when the layer has so few tiles that
+// half the SMs or more would idle and K is long enough to share (each range about 2048 wide or more, a multiple of
+// 256: below that the second launch, which adds the ranges, costs more than the shorter loop saves).
+int tcgen05_k_splits(int64_t M, int64_t N, int64_t K, int64_t* split_k) {
+    const int64_t m_tiles = (M + kMaxBN - 1) / kMaxBN;
+    const int64_t tiles = m_tiles * ((N + kBM - 1) / kBM);
+    int64_t splits = tiles > 0 ? std::min<int64_t>(4, 148 / tiles) : 1;
+    splits = std::max<int64_t>(1, std::min<int64_t>(splits, K / 2048));
+    int64_t width = ((K + splits - 1) / splits + 255) / 256 * 256;
+    splits = (K + width - 1) / width;
+    if (split_k != nullptr) *split_k = splits > 1 ? width : K;
+    return static_cast<int>(splits);
+}
+
+size_t tcgen05_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    const int splits = tcgen05_k_splits(M, N, K, nullptr);
+    return splits > 1 ? linear_workspace_bytes_for(M, N, splits) : 0;
+}
+
 int launch_linear_tcgen05(const LinearProblem& prob, cudaStream_t stream) {
     if (prob.group != kGroup || prob.K % kGroup != 0 || prob.K <= 0) return W4A16_ERR_BAD_CONFIG;
     if (prob.M > INT32_MAX || prob.N > INT32_MAX || prob.K > INT32_MAX) return W4A16_ERR_TOO_LARGE;
@@ -516,6 +565,20 @@ int launch_linear_tcgen05(const LinearProblem& prob, cudaStream_t stream) {
                     static_cast<int>(prob.M), static_cast<int>(prob.N), static_cast<int>(prob.K),
                     static_cast<int>(bn), static_cast<int>(m_tiles), static_cast<int>(n_tiles),
                     static_cast<int>(m_tiles * n_tiles), 0};
+    // K split across CTAs when the caller's workspace has room for the partial sums (they follow the counter prefix
+    // that the streaming kernel keeps at zero there)
+    int64_t split_k = prob.K;
+    int splits = tcgen05_k_splits(prob.M, prob.N, prob.K, &split_k);
+    if (splits > 1 && (prob.workspace == nullptr || reinterpret_cast<uintptr_t>(prob.workspace) % 16 != 0 ||
+                       prob.workspace_bytes < linear_workspace_bytes_for(prob.M, prob.N, splits))) {
+        splits = 1;
+        split_k = prob.K;
+    }
+    params.k_splits = splits;
+    params.split_k = static_cast<int>(split_k);
+    params.partial = splits > 1 ? reinterpret_cast<float*>(static_cast<char*>(prob.workspace) + linear_counter_bytes(prob.M, prob.N))
+                                : nullptr;
+    params.total_tiles *= splits;
     // as many operand stages as fit beside the code ring: 4 with a 256-row batch tile, 8 up to 80 rows
     const size_t fixed = static_cast<size_t>(kCodeSlots) * kPackedTileBytes + 1024 /* alignment slack */ + kBarrierBytes;
     const size_t sub_bytes = kASubTileBytes + static_cast<size_t>(bn) * (kBK * 2);      // A and x sub-tile
@@ -550,6 +613,10 @@ int launch_linear_tcgen05(const LinearProblem& prob, cudaStream_t stream) {
     void* args[] = {&params, &x_map, &w_map};
     if (cudaLaunchKernel(kernel, dim3(grid), dim3(kThreadsTc), args, smem, stream) != cudaSuccess) return W4A16_ERR_LAUNCH;
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
+    if (splits > 1) {
+        // y = half(sum of the ranges, in order)
+        return launch_sum_partials(params.partial, static_cast<__half*>(prob.y), prob.M * prob.N, splits, nullptr, false, stream);
+    }
     return W4A16_OK;
 }
 

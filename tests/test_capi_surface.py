@@ -79,10 +79,12 @@ def test_workspace_size_query():
     assert lib.w4a16_linear_workspace_bytes_flags(1, 1024, 8192, _native.FLAG_FORCE_GENERIC) == 0
     assert lib.w4a16_linear_workspace_bytes_flags(16, 8192, 8192, 0) == lib.w4a16_linear_workspace_bytes(16, 8192, 8192) > 1 << 20
     # 17..64 rows: large layers go to the GEMM as well (no scratch), small ones stay on the streaming kernel
-    assert lib.w4a16_linear_workspace_bytes(32, 8192, 8192) == 0
+    # (the GEMM wants scratch of its own only for layers of few tiles, to share their K between CTAs: 64 tiles here)
+    assert 0 < lib.w4a16_linear_workspace_bytes(32, 8192, 8192) < 3 << 20
     assert lib.w4a16_linear_workspace_bytes_flags(32, 8192, 8192, _native.FLAG_NO_TCGEN05) > 4 << 20
     assert lib.w4a16_linear_workspace_bytes(32, 1024, 8192) > 0
-    assert lib.w4a16_linear_workspace_bytes_flags(8, 1024, 8192, _native.FLAG_FORCE_TCGEN05) == 0
+    assert lib.w4a16_linear_workspace_bytes_flags(8, 28672, 8192, _native.FLAG_FORCE_TCGEN05) == 0
+    assert lib.w4a16_linear_workspace_bytes_flags(8, 1024, 8192, _native.FLAG_FORCE_TCGEN05) == 256 * 1024 + 4 * 8 * 1024 * 4
 
 
 def test_missing_library_is_an_error(monkeypatch, tmp_path):

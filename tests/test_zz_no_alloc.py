@@ -66,7 +66,10 @@ def test_batches_that_need_no_scratch_are_forwarded(m, n, k):
     """From 65 rows on the ordinary entry point runs the tcgen05 GEMM, which has no split-K scratch, so the
     allocation-free entry point must run such batches too, whatever their size, and give the same bits."""
     lib = _native.core()
-    assert lib.w4a16_linear_workspace_bytes_flags(m, n, k, 0) == 0
+    # (no scratch at all, or -- a layer of few tiles, whose K the GEMM would share between CTAs -- more than the
+    # built-in array holds, in which case the GEMM runs unsplit)
+    need = lib.w4a16_linear_workspace_bytes_flags(m, n, k, 0)
+    assert need == 0 or need > lib.w4a16_static_scratch_bytes()
     torch.manual_seed(m + n)
     packed = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda")
     scales = (torch.rand((n, k // 128), device="cuda") * 0.01 + 1e-3).half()
