@@ -486,6 +486,26 @@ linear_tcgen05_kernel(const TcParams p, const __grid_constant__ CUtensorMap x_ma
     }
 }
 
+// y = half(sum of the K ranges' partial sums, in range order): four outputs per thread, 16-byte loads.
+__global__ void sum_ranges_kernel(const float* __restrict__ partial, __half* __restrict__ y, long long count, int ranges) {
+    const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+    if (i >= count) return;
+    float4 sum = __ldcg(reinterpret_cast<const float4*>(partial + i));
+    for (int r = 1; r < ranges; ++r) {
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(partial + static_cast<long long>(r) * count + i));
+        sum.x += v.x;
+        sum.y += v.y;
+        sum.z += v.z;
+        sum.w += v.w;
+    }
+    const __half2 lo = __floats2half2_rn(sum.x, sum.y);
+    const __half2 hi = __floats2half2_rn(sum.z, sum.w);
+    uint2 out;
+    out.x = *reinterpret_cast<const uint32_t*>(&lo);
+    out.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(y + i) = out;
+}
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -615,7 +635,15 @@ int launch_linear_tcgen05(const LinearProblem& prob, cudaStream_t stream) {
     g_launch_count.fetch_add(1, std::memory_order_relaxed);
     if (splits > 1) {
         // y = half(sum of the ranges, in order)
-        return launch_sum_partials(params.partial, static_cast<__half*>(prob.y), prob.M * prob.N, splits, nullptr, false, stream);
+        const long long count = static_cast<long long>(prob.M) * prob.N;
+        if (count % 4 != 0 || reinterpret_cast<uintptr_t>(prob.y) % 8 != 0) {
+            return launch_sum_partials(params.partial, static_cast<__half*>(prob.y), count, splits, nullptr, false, stream);
+        }
+        const long long blocks = (count / 4 + 255) / 256;
+        if (blocks > INT32_MAX) return W4A16_ERR_TOO_LARGE;
+        sum_ranges_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(params.partial, static_cast<__half*>(prob.y), count, splits);
+        if (cudaGetLastError() != cudaSuccess) return W4A16_ERR_LAUNCH;
+        g_launch_count.fetch_add(1, std::memory_order_relaxed);
     }
     return W4A16_OK;
 }
