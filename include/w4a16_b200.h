@@ -74,8 +74,8 @@ typedef struct w4a16_linear_config {
  * Replaces the reference's int4_linear_cuda (csrc/int4_linear_kernel.cu:641-802) and the kernels
  * it dispatches to (decode_multirow :325-404, small_batch :542-617, naive :20-69).
  *
- * Fast path when group_size == 128 and x, packed are 16-byte aligned: M <= 16 runs the mma.sync
- * streaming kernel, M >= 65 (and 17..64 on layers of N >= 4096 where a cost model built from measurements
+ * Fast path when group_size == 128 and x, packed are 16-byte aligned: M <= 8 runs the mma.sync
+ * streaming kernel, M >= 65 (and 9..64 on layers of N >= 4096 where a cost model built from measurements
  * favours it) a tcgen05 GEMM whose producer warps dequantise into the operand tiles
  * (no FP16 weight matrix in memory; weights enter the product as half(code * scale), the arithmetic of
  * the reference's dequantise-then-matmul prefill route, w4a16/linear.py:132-152).

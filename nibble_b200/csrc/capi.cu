@@ -33,7 +33,7 @@ bool fast_path_applies(const void* x, const void* packed, int64_t K, int64_t gro
 namespace {
 
 // Whether a fast-path call with FP16 output goes to the tcgen05 GEMM rather than the streaming kernel.
-// From 65 rows on always.  Between 17 and 64 rows the streaming kernel still wins on small layers, but its cost
+// From 65 rows on always, up to 8 rows never.  Between 9 and 64 rows the streaming kernel still wins on small layers, but its cost
 // grows with the batch and with K (every CTA stages batch x K activations, K is split ever further and the partial
 // sums travel through memory) while the GEMM's does not.  Both sides of the comparison are fits to measurements
 // on B200: the GEMM takes about 0.6 us per 128-wide K step of a round of 148 weight tiles whatever the batch; the
@@ -42,8 +42,8 @@ namespace {
 bool routes_to_tcgen05(int64_t M, int64_t N, int64_t K, uint32_t flags) {
     if (flags & (W4A16_FLAG_OUTPUT_F32 | W4A16_FLAG_NO_TCGEN05 | W4A16_FLAG_FORCE_GENERIC)) return false;
     if ((flags & W4A16_FLAG_FORCE_TCGEN05) || M >= w4a16::kTcgen05MinRows) return true;
-    if (M <= 16 || N < 4096) return false;
-    const double padded = M <= 32 ? 32.0 : 64.0;
+    if (M <= 8 || N < 4096) return false;
+    const double padded = M <= 16 ? 16.0 : M <= 32 ? 32.0 : 64.0;
     const double giga_macs = padded * static_cast<double>(K) * static_cast<double>(N) * 1e-9;
     const double streaming_us = 5.0 + giga_macs * (8.0 + 1.5 * static_cast<double>(K) / 1024.0);
     const int64_t rounds = ((N + 127) / 128 + 147) / 148;
@@ -51,7 +51,8 @@ bool routes_to_tcgen05(int64_t M, int64_t N, int64_t K, uint32_t flags) {
     const int splits = w4a16::tcgen05_k_splits(M, N, K, nullptr);
     const double gemm_us = 3.5 + 0.6 * static_cast<double>(rounds) * static_cast<double>(K) / (128.0 * splits) +
                            (splits > 1 ? 3.0 : 0.0);
-    return gemm_us < streaming_us;
+    // 9..16 rows are close to the streaming kernel's best case: only a clear win moves them (K = 28672: 94 -> 71 us)
+    return gemm_us < (M <= 16 ? 0.85 : 1.0) * streaming_us;
 }
 
 }  // namespace

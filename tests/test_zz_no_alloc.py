@@ -90,7 +90,7 @@ def test_scratch_size_is_reported_and_oversized_problems_are_refused():
     capacity = lib.w4a16_static_scratch_bytes()
     assert capacity == 4 * 2**20
     # A problem that wants split-K scratch beyond the built-in array is refused, nothing launched.
-    m, n, k = 16, 8192, 28672      # sixteen rows stay on the streaming kernel; K this long is split eight ways
+    m, n, k = 16, 32768, 8192      # sixteen rows of this layer stay on the streaming kernel, K split four ways
     assert lib.w4a16_linear_workspace_bytes(m, n, k) > capacity
     before = lib.w4a16_launch_count()
     x = torch.zeros((m, k), dtype=torch.float16, device="cuda")
