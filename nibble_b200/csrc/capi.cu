@@ -42,7 +42,18 @@ namespace {
 bool routes_to_tcgen05(int64_t M, int64_t N, int64_t K, uint32_t flags) {
     if (flags & (W4A16_FLAG_OUTPUT_F32 | W4A16_FLAG_NO_TCGEN05 | W4A16_FLAG_FORCE_GENERIC)) return false;
     if ((flags & W4A16_FLAG_FORCE_TCGEN05) || M >= w4a16::kTcgen05MinRows) return true;
-    if (M <= 8 || N < 4096) return false;
+    if (M <= 8) return false;
+    if (N < 4096) {
+        // Narrow layers: the fits below do not hold (few row tiles, so the streaming kernel leans on K splits whose
+        // partial sums and repeated activation staging grow with the batch).  Measured: with K = 5632, N = 2048 the
+        // GEMM, sharing K between CTAs, takes 14-15 us at 24..64 rows where the streaming kernel takes 22-42 us;
+        // with K = 2048 the streaming kernel wins throughout.  So: from 17 rows on, when the streaming kernel
+        // would split K four ways or more and the layer has at least eight weight tiles.
+        // (with N = 1024 and K = 8192 the streaming kernel is still ahead at 17..32 rows, 14-15 us against 18 us,
+        // and behind from 33 on, 24 us against 19 us)
+        if (M <= 16 || N < 1024 || K < 4096 || (N < 2048 && M <= 32)) return false;
+        return w4a16::choose_linear_config(M, N, K, w4a16::kMaxKSplits).k_splits >= 4;
+    }
     const double padded = M <= 16 ? 16.0 : M <= 32 ? 32.0 : 64.0;
     const double giga_macs = padded * static_cast<double>(K) * static_cast<double>(N) * 1e-9;
     const double streaming_us = 5.0 + giga_macs * (8.0 + 1.5 * static_cast<double>(K) / 1024.0);

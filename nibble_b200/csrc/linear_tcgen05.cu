@@ -527,13 +527,13 @@ EncodeTiledFn tensor_map_encoder() {
 }  // namespace
 
 // K ranges per output tile that the GEMM wants for a problem: more than one when the layer has so few tiles that
-// half the SMs or more would idle and K is long enough to share (each range about 2048 wide or more, a multiple of
-// 256: below that the second launch, which adds the ranges, costs more than the shorter loop saves).
+// half the SMs or more would idle and K is long enough to share (ranges of 1024 or more, a multiple of 256, and
+// K of 4096 or more: below that the second launch, which adds the ranges, costs more than the shorter loop saves).
 int tcgen05_k_splits(int64_t M, int64_t N, int64_t K, int64_t* split_k) {
     const int64_t m_tiles = (M + kMaxBN - 1) / kMaxBN;
     const int64_t tiles = m_tiles * ((N + kBM - 1) / kBM);
     int64_t splits = tiles > 0 ? std::min<int64_t>(4, 148 / tiles) : 1;
-    splits = std::max<int64_t>(1, std::min<int64_t>(splits, K / 2048));
+    splits = std::max<int64_t>(1, std::min<int64_t>(splits, K / (K >= 4096 ? 1024 : 2048)));
     int64_t width = ((K + splits - 1) / splits + 255) / 256 * 256;
     splits = (K + width - 1) / width;
     if (split_k != nullptr) *split_k = splits > 1 ? width : K;

@@ -85,6 +85,7 @@ def test_workspace_size_query():
     assert lib.w4a16_linear_workspace_bytes(32, 1024, 8192) > 0
     assert lib.w4a16_linear_workspace_bytes_flags(8, 28672, 8192, _native.FLAG_FORCE_TCGEN05) == 0
     assert lib.w4a16_linear_workspace_bytes_flags(8, 1024, 8192, _native.FLAG_FORCE_TCGEN05) == 256 * 1024 + 4 * 8 * 1024 * 4
+    assert lib.w4a16_linear_workspace_bytes_flags(128, 256, 2048, _native.FLAG_FORCE_TCGEN05) == 0    # K below 4096 is not shared
 
 
 def test_missing_library_is_an_error(monkeypatch, tmp_path):

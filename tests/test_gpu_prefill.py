@@ -127,10 +127,10 @@ def test_batch_too_large_for_the_streaming_kernel_without_scratch_takes_the_gemm
 
 
 @pytest.mark.parametrize(("m", "k", "n"), [
-    (65, 4096, 256),       # 2 tiles: two K ranges of 2048 (ranges are not made shorter than that)
+    (65, 4096, 256),       # 2 tiles: four K ranges of 1024 (ranges are not made shorter than that)
     (65, 4096, 250),       # the same with M x N not a multiple of four: the element-wise sum kernel
-    (128, 4096, 1024),     # 8 tiles: two ranges
-    (100, 4352, 640),      # 5 tiles, K = 17 x 256: ranges of 2304 and 2048 (the last one shorter)
+    (128, 4096, 1024),     # 8 tiles: four ranges
+    (100, 4352, 640),      # 5 tiles, K = 17 x 256: three ranges of 1280 and one of 512
     (300, 8192, 512),      # two batch tiles (64-wide stages), 8 tiles in all: four ranges of 2048
     (32, 8192, 4096),      # a medium batch on the forced GEMM: 32 tiles, four ranges
 ])
